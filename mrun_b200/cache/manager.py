@@ -132,7 +132,7 @@ def token_bytes(needs: Sequence[object], shares: Sequence[Optional[int]], elemen
             continue
         paged, states = split_need(need)
         if isinstance(paged, PagedKV):
-            per_token += 2 * paged.kv_heads * paged.head_dim * element_size
+            per_token += paged.kv_heads * (paged.head_dim + (paged.value_dim or paged.head_dim)) * element_size
         elif isinstance(paged, PagedLatent):
             per_token += paged.width * element_size
         elif isinstance(paged, PagedMaps):
@@ -217,9 +217,9 @@ class CacheManager:
                     v = torch.zeros((paged.value_chunks, num_pages, paged.kv_heads, page_size,
                                      paged.value_chunk_dim), dtype=dtype, device=device)
                 else:
-                    shape = (num_pages, paged.kv_heads, page_size, paged.head_dim)
-                    k = torch.zeros(shape, dtype=dtype, device=device)
-                    v = torch.zeros(shape, dtype=dtype, device=device)
+                    shape = (num_pages, paged.kv_heads, page_size)
+                    k = torch.zeros(shape + (paged.head_dim,), dtype=dtype, device=device)
+                    v = torch.zeros(shape + (paged.value_dim or paged.head_dim,), dtype=dtype, device=device)
             self.entries.append(EntryCache(paged, key, True, k=k, v=v, state=first_state, states=states))
 
         # the books: pools, block tables, lengths, plans (csrc/host/cache_core.cpp)
@@ -272,7 +272,7 @@ class CacheManager:
             if isinstance(entry.need, PagedMaps):
                 total += (entry.k[:, 0].numel() + entry.v[:, 0].numel()) * entry.k.element_size()
             elif isinstance(entry.need, (PagedKV, PagedLatent)):
-                total += (1 if entry.v is entry.k else 2) * entry.k[0].numel() * entry.k.element_size()
+                total += (entry.k[0].numel() + (0 if entry.v is entry.k else entry.v[0].numel())) * entry.k.element_size()
         return total
 
     # ------------------------------------------------------------------ requests

@@ -14,11 +14,13 @@ from typing import Optional, Tuple
 
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values of every token (``window`` None) or of the last ``window`` tokens."""
+    """Keys and values of every token (``window`` None) or of the last ``window`` tokens.
+    ``value_dim``: the values' feature size where it differs from the keys' (``head_dim``)."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
 
     def group_key(self) -> tuple:
         return ("paged", self.window)

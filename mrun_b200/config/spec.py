@@ -47,6 +47,8 @@ class RMSNormSpec:
     bare: bool = False
     # the checkpoint holds one number for all coordinates (a tensor without dimensions)
     scalar: bool = False
+    # the checkpoint stores the scale vector minus this number (weights kept around zero: 1.0)
+    offset: float = 0.0
 
 
 # --------------------------------------------------------------------------- position encodings
@@ -71,13 +73,15 @@ class ScaledRotarySpec:
     (2 pi t)) / (2 ln base) is the (fractional) pair that makes t turns over ``original``
     positions; lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), dims - 1), r_i = clamp((i - lo)
     / max(hi - lo, 0.001), 0, 1); the frequency becomes f_i / factor * r_i + f_i * (1 - r_i), and
-    cos and sin are both multiplied by 0.1 * ln(factor) + 1."""
+    cos and sin are both multiplied by 0.1 * ln(factor) + 1.  ``linear_factor`` divides every
+    frequency (positions stretched evenly), before any band-wise stretch."""
 
     kind: ClassVar[str] = "rotary_scaled"
     dims: int
     base: float
     pairing: str = "interleaved"
     scaling: Optional[Tuple[float, float, float, float]] = None
+    linear_factor: Optional[float] = None
 
 
 # --------------------------------------------------------------------------- mixers
@@ -146,6 +150,54 @@ class DifferentialAttentionSpec:
     eps: float
     position: Optional[Any] = None
     window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class GatedAttentionSpec:
+    """Grouped-query softmax attention whose keys (``dim`` a head) and values (``vdim`` a head)
+    may differ in size, with three options.  ``qk_norm`` = ``"projection"``: q and k are each
+    divided by the root mean square over the whole projection (all heads together, ``eps`` inside
+    the root) and multiplied by a weight of that size, before the rotation; None: no norm.
+    ``sink``: the softmax has one more term of score 0 and no value, p_j = exp(s_j) / (1 + sum
+    exp(s)).  ``head_gate``: head h's output is multiplied by sigmoid(g x)_h, one projection row a
+    head.  ``own_kv`` False: the layer has no key and value projections and reads the pages of
+    another schedule entry (``ScheduleEntry.cache_of``), with queries, gate and output of its
+    own."""
+
+    kind: ClassVar[str] = "gated_attention"
+    hidden: int
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    softmax_scale: float
+    eps: float
+    qk_norm: Optional[str] = "projection"
+    sink: bool = True
+    head_gate: bool = True
+    own_kv: bool = True
+    position: Optional[Any] = None
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """Linear attention with a decay per head and key channel and a state of fixed size: q
+    (times dim^-1/2), k (``heads`` x ``dim``) and v (``heads`` x ``vdim``) are projections; the
+    decay is sigmoid(a2 (a1 x) + bias)^(1 / ``tau``), a low-rank projection of inner size
+    ``rank``.  Per head S_t = diag(decay_t) S_(t-1) + k_t v_t^T (the decay multiplies the rows
+    that belong to key channels), o_t = S_t^T q_t.  Every head's o is RMS-normed over ``vdim``
+    with a weight the heads share, the heads together are multiplied by SiLU of a gate
+    projection and projected out."""
+
+    kind: ClassVar[str] = "gated_linear_attention"
+    hidden: int
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+    rank: int
+    eps: float
 
 
 @dataclass(frozen=True)
@@ -222,6 +274,31 @@ class RoutedMLPSpec:
 
 
 @dataclass(frozen=True)
+class GroupedRoutedMLPSpec:
+    """A mixture of ``experts`` gated feed-forwards ``down(act(gate x) * up x)`` without biases,
+    chosen by a router whose scores are sigmoid(router x) in 32-bit.  The experts form ``groups``
+    equal groups of neighbours; a group's score is the sum of its ``group_top`` largest scores and
+    only experts of the ``keep_groups`` best groups can be chosen (``groups`` = 1: no limit).
+    Each token takes the ``top`` allowed experts with the largest scores; their weights are the
+    scores divided by their sum (+ 1e-20) times ``route_scale``.  ``shared_ff`` > 0: one more
+    expert of that size runs for every token, weighed by sigmoid(sg x) (one number a token) when
+    ``shared_gate``, else by 1."""
+
+    kind: ClassVar[str] = "grouped_routed_mlp"
+    hidden: int
+    experts: int
+    top: int
+    expert_ff: int
+    groups: int = 1
+    keep_groups: int = 1
+    group_top: int = 2
+    route_scale: float = 1.0
+    shared_ff: int = 0
+    shared_gate: bool = True
+    activation: str = "silu"
+
+
+@dataclass(frozen=True)
 class TableRoutedMLPSpec:
     """A mixture of ``experts`` gated feed-forwards without a router: row ``token id`` of an
     integer table [``vocab``, ``top``] names the token's experts, each weighing 1 / ``top``.
@@ -254,6 +331,23 @@ class ScaleSpec:
 
     kind: ClassVar[str] = "scale"
     factor: float
+
+
+@dataclass(frozen=True)
+class HashedBigramEmbeddingSpec:
+    """Token embedding times ``scale`` plus a row of a second table chosen by the token and the
+    one before it: row (previous * ``mul_prev`` + token * ``mul_cur``) mod ``buckets``, and row
+    ``buckets`` (the table's last) for a sequence's first token.  ``buckets`` = 0: no second table.
+    The previous token is per-request state."""
+
+    kind: ClassVar[str] = "hashed_bigram_embedding"
+    vocab: int
+    hidden: int
+    scale: float = 1.0
+    buckets: int = 0
+    mul_prev: int = 0
+    mul_cur: int = 0
+    table_name: str = "bigram"
 
 
 # --------------------------------------------------------------------------- layers and model
@@ -320,6 +414,9 @@ class ModelSpec:
     # the float32 logits of the wanted rows
     embedding_transform: Any = None
     logits_transform: Any = None
+    # an embedding part (kinds of the ``EMBEDDINGS`` registry) in place of the plain table
+    # lookup; it binds ``embedding_name`` itself and may keep per-request state
+    embedding: Any = None
     # residual streams a token (layers of the ``streams`` arrangement); 1: the plain residual row
     streams: int = 1
     # tensors that may be present in a checkpoint and are dropped unread: the vision tower, heads

@@ -10,6 +10,11 @@
 // Math: s = scale * q·k, p = softmax(s), o = p·v; query head h reads kv head h / (heads/kv_heads)
 // (crates/mrun-engine/src/models/common.rs:129,199-205; causal alignment to the end of the keys,
 // crates/mrun-engine/src/tensor/nuvec.rs:866-872).
+//
+// Options: values of another size than the keys (value pages [pages, kv_heads, page_size,
+// value_dim]); a sink, one more term of score 0 without a value in the softmax's denominator (the
+// running maximum starts at 0 and the running sum at 1); a gate per (token, head), whose sigmoid
+// multiplies the head's output.
 #include "common.cuh"
 
 using namespace mrun;
@@ -24,8 +29,8 @@ paged_attention_generic_kernel(const TA* __restrict__ q, long q_stride, TA* __re
                                const TA* __restrict__ k_cache, const TA* __restrict__ v_cache,
                                const int* __restrict__ block_tables, int max_blocks,
                                const int* __restrict__ token_slot, const int* __restrict__ positions,
-                               int heads, int kv_heads, int head_dim, int page_size, float scale,
-                               int window) {
+                               int heads, int kv_heads, int head_dim, int value_dim, int page_size, float scale,
+                               int window, int sink, const TA* __restrict__ gate, long gate_stride) {
     extern __shared__ float smem[];
     float* qs = smem;                 // head_dim
     float* probs = qs + head_dim;     // THREADS
@@ -34,9 +39,9 @@ paged_attention_generic_kernel(const TA* __restrict__ q, long q_stride, TA* __re
 
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int pos = positions[t];
-    TA* dst = out + ((size_t)t * heads + h) * head_dim;
+    TA* dst = out + ((size_t)t * heads + h) * value_dim;
     if (pos < 0) {  // padding token
-        for (int d = tid; d < head_dim; d += THREADS) dst[d] = from_float<TA>(0.f);
+        for (int d = tid; d < value_dim; d += THREADS) dst[d] = from_float<TA>(0.f);
         return;
     }
     const int kvh = h / (heads / kv_heads);
@@ -46,8 +51,8 @@ paged_attention_generic_kernel(const TA* __restrict__ q, long q_stride, TA* __re
     __syncthreads();
 
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    float m = -INFINITY, l = 0.f;
-    float acc[8];  // head_dim <= 8 * THREADS = 1024
+    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+    float acc[8];  // value_dim <= 8 * THREADS = 1024
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 
@@ -76,40 +81,46 @@ paged_attention_generic_kernel(const TA* __restrict__ q, long q_stride, TA* __re
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int d = tid + i * THREADS;
-            if (d < head_dim) {
+            if (d < value_dim) {
                 float a = acc[i] * corr;
                 for (int j = 0; j < n; ++j)
-                    a = fmaf(probs[j], to_float(v_cache[(long)rows[j] * head_dim + d]), a);
+                    a = fmaf(probs[j], to_float(v_cache[(long)rows[j] * value_dim + d]), a);
                 acc[i] = a;
             }
         }
         __syncthreads();
     }
-    const float inv = 1.f / l;
+    float inv = 1.f / l;
+    if (gate) inv *= 1.f / (1.f + expf(-to_float(gate[(size_t)t * gate_stride + h])));
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int d = tid + i * THREADS;
-        if (d < head_dim) dst[d] = from_float<TA>(acc[i] * inv);
+        if (d < value_dim) dst[d] = from_float<TA>(acc[i] * inv);
     }
 }
 
 }  // namespace
 
 // q: row t starts at q + t * q_stride, heads contiguous [heads, head_dim].
-// out: dense [tokens, heads * head_dim].  caches: [pages, kv_heads, page_size, head_dim].
+// out: dense [tokens, heads * value_dim].  key pages: [pages, kv_heads, page_size, head_dim]; value
+// pages: [pages, kv_heads, page_size, value_dim].  gate: row t at gate + t * gate_stride, one
+// entry a head, or null.
 // block_tables: [slots, max_blocks], one row per state slot; token_slot[t] picks the row; positions[t] < 0 = padding.
 MRUN_API int mrun_paged_attention_generic(const void* q, long q_stride, void* out, const void* k_cache,
                                           const void* v_cache, int act_dtype, const int* block_tables,
                                           int max_blocks, const int* token_slot, const int* positions,
-                                          int tokens, int heads, int kv_heads, int head_dim,
-                                          int page_size, long cache_rows, float scale, int window,
-                                          cudaStream_t stream) {
+                                          int tokens, int heads, int kv_heads, int head_dim, int value_dim,
+                                          int page_size, long cache_rows, float scale, int window, int sink,
+                                          const void* gate, long gate_stride, cudaStream_t stream) {
     MRUN_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && head_dim > 0 && page_size > 0 && max_blocks > 0,
                  "paged_attention_generic: bad sizes");
     MRUN_REQUIRE(heads % kv_heads == 0, "paged_attention_generic: heads=%d is not a multiple of kv_heads=%d",
                  heads, kv_heads);
     MRUN_REQUIRE(head_dim <= 8 * THREADS, "paged_attention_generic: head_dim=%d exceeds the supported %d",
                  head_dim, 8 * THREADS);
+    MRUN_REQUIRE(value_dim > 0 && value_dim <= 8 * THREADS, "paged_attention_generic: value_dim=%d outside 1 .. %d",
+                 value_dim, 8 * THREADS);
+    MRUN_REQUIRE(gate == nullptr || gate_stride >= heads, "paged_attention_generic: the gate's row stride is below the heads");
     MRUN_REQUIRE(heads <= 65535, "paged_attention_generic: heads=%d exceeds 65535", heads);
     MRUN_REQUIRE(cache_rows < (1L << 31), "paged_attention_generic: the cache has %ld rows, the limit is 2^31",
                  cache_rows);
@@ -120,13 +131,13 @@ MRUN_API int mrun_paged_attention_generic(const void* q, long q_stride, void* ou
     if (act_dtype == MRUN_F32)
         paged_attention_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
             (const float*)q, q_stride, (float*)out, (const float*)k_cache, (const float*)v_cache,
-            block_tables, max_blocks, token_slot, positions, heads, kv_heads, head_dim, page_size, scale,
-            window);
+            block_tables, max_blocks, token_slot, positions, heads, kv_heads, head_dim, value_dim, page_size, scale,
+            window, sink, (const float*)gate, gate_stride);
     else if (act_dtype == MRUN_BF16)
         paged_attention_generic_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
             (const __nv_bfloat16*)v_cache, block_tables, max_blocks, token_slot, positions, heads, kv_heads,
-            head_dim, page_size, scale, window);
+            head_dim, value_dim, page_size, scale, window, sink, (const __nv_bfloat16*)gate, gate_stride);
     else
         return mrun_set_error("paged_attention_generic: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("paged_attention_generic");

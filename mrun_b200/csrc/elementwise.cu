@@ -428,6 +428,124 @@ MRUN_API int mrun_qk_norm_rope_cache(void* qkv, int act_dtype, const float* q_we
 }
 
 // ------------------------------------------------------------------------------------------
+// RMS norm of q and of k over the whole projection (all heads of a token together, one weight per
+// feature, eps inside the root), rotation of the first rotary_dim features of every q and k head,
+// write of k and v into pages whose key and value sizes may differ.
+//   x: row t at x + t * ld; the q heads ([heads, dim]) start at column q_off, the k heads
+//   ([kv_heads, dim]) at k_off, the v heads ([kv_heads, vdim]) at v_off.  k_off < 0: the row has no
+//   keys and values (a layer that reads another layer's pages) and only q is worked on.
+//   q is normed and rotated in place.  k (normed, rotated) and v (as is) go to the pages at
+//   slots[t]; a negative slot skips the write.  pairing: 0 = feature i with i + rotary_dim/2,
+//   1 = feature 2i with 2i + 1; rot holds (cos, sin) per token and pair.
+// One block a token; the token's q and k rows are staged in shared memory in 32-bit.
+// ------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(256)
+proj_norm_rope_cache_kernel(TA* __restrict__ x, long ld, long q_off, long k_off, long v_off,
+                            const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                            const float2* __restrict__ rot, int rotary_dim, int pairing,
+                            const int* __restrict__ slots, TA* __restrict__ k_cache, TA* __restrict__ v_cache,
+                            int heads, int kv_heads, int dim, int vdim, int page_size) {
+    extern __shared__ float staged[];         // heads * dim, then kv_heads * dim
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    TA* row = x + (size_t)t * ld;
+    const int nq = heads * dim, nk = kv_heads * dim;
+    const int slot = slots ? slots[t] : -1;
+    const bool own = k_off >= 0 && slot >= 0;
+    float* qv = staged;
+    float* kv = staged + nq;
+
+    float ss = 0.f;
+    for (int e = tid; e < nq; e += blockDim.x) {
+        const float v = to_float(row[q_off + e]);
+        qv[e] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    if (q_weight) {
+        const float inv = 1.f / sqrtf(ss / (float)nq + eps);
+        for (int e = tid; e < nq; e += blockDim.x) qv[e] = qv[e] * inv * q_weight[e];
+    }
+    if (own) {
+        float sk = 0.f;
+        for (int e = tid; e < nk; e += blockDim.x) {
+            const float v = to_float(row[k_off + e]);
+            kv[e] = v;
+            sk = fmaf(v, v, sk);
+        }
+        sk = block_sum(sk, scratch);
+        if (k_weight) {
+            const float inv = 1.f / sqrtf(sk / (float)nk + eps);
+            for (int e = tid; e < nk; e += blockDim.x) kv[e] = kv[e] * inv * k_weight[e];
+        }
+    }
+    __syncthreads();
+
+    const int half = rotary_dim >> 1;
+    const float2* cs = rot ? rot + (size_t)t * half : nullptr;
+    auto rotated = [&](const float* head, int e) -> float {
+        if (!cs || e >= rotary_dim) return head[e];
+        int pair, partner;
+        bool first;
+        if (pairing) { pair = e >> 1; partner = e ^ 1; first = (e & 1) == 0; }
+        else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
+        const float2 c = cs[pair];
+        return first ? head[e] * c.x - head[partner] * c.y : head[e] * c.x + head[partner] * c.y;
+    };
+    for (int i = tid; i < nq; i += blockDim.x) {
+        const int h = i / dim, e = i - h * dim;
+        row[q_off + i] = from_float<TA>(rotated(qv + h * dim, e));
+    }
+    if (!own) return;
+    const int page = slot / page_size, off = slot - page * page_size;
+    for (int i = tid; i < nk; i += blockDim.x) {
+        const int g = i / dim, e = i - g * dim;
+        k_cache[(((size_t)page * kv_heads + g) * page_size + off) * dim + e] = from_float<TA>(rotated(kv + g * dim, e));
+    }
+    for (int i = tid; i < kv_heads * vdim; i += blockDim.x) {
+        const int g = i / vdim, e = i - g * vdim;
+        v_cache[(((size_t)page * kv_heads + g) * page_size + off) * vdim + e] = row[v_off + i];
+    }
+}
+
+MRUN_API int mrun_proj_norm_rope_cache(void* x, long ld, long q_off, long k_off, long v_off, int act_dtype,
+                                       const float* q_weight, const float* k_weight, float eps, const float* rot,
+                                       int rotary_dim, int pairing, const int* slots, void* k_cache, void* v_cache,
+                                       int tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
+                                       cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && page_size > 0,
+                 "proj_norm_rope_cache: bad sizes");
+    MRUN_REQUIRE(rotary_dim >= 0 && rotary_dim <= dim && rotary_dim % 2 == 0,
+                 "proj_norm_rope_cache: rotary_dim=%d must be even and at most dim=%d", rotary_dim, dim);
+    MRUN_REQUIRE(q_off >= 0 && (k_off < 0 || v_off >= 0), "proj_norm_rope_cache: bad column offsets");
+    MRUN_REQUIRE(k_off < 0 || slots == nullptr || (k_cache && v_cache), "proj_norm_rope_cache: slots without a cache");
+    const size_t smem = (size_t)(heads + kv_heads) * dim * sizeof(float);
+    MRUN_REQUIRE(smem <= 200 * 1024, "proj_norm_rope_cache: %d q and k features a token exceed the supported 51200",
+                 (heads + kv_heads) * dim);
+    if (tokens == 0) return 0;
+    const float2* cs = rotary_dim ? (const float2*)rot : nullptr;
+    if (act_dtype == MRUN_F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(proj_norm_rope_cache_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        proj_norm_rope_cache_kernel<float><<<tokens, 256, smem, stream>>>(
+            (float*)x, ld, q_off, k_off, v_off, q_weight, k_weight, eps, cs, rotary_dim, pairing, slots, (float*)k_cache,
+            (float*)v_cache, heads, kv_heads, dim, vdim, page_size);
+    } else if (act_dtype == MRUN_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(proj_norm_rope_cache_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem);
+        proj_norm_rope_cache_kernel<__nv_bfloat16><<<tokens, 256, smem, stream>>>(
+            (__nv_bfloat16*)x, ld, q_off, k_off, v_off, q_weight, k_weight, eps, cs, rotary_dim, pairing, slots,
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, dim, vdim, page_size);
+    } else {
+        return mrun_set_error("proj_norm_rope_cache: unknown dtype code %d", act_dtype);
+    }
+    MRUN_CHECK_LAUNCH("proj_norm_rope_cache");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
 // Gated activation: out[t, i] = act(gate_i) * up_i in 32-bit; act by code: SiLU
 // (z * sigmoid(z), crates/mrun-engine/src/models/activations.rs:46-59) or tanh-GELU.
 // Layout of gate_up[t, :]: block == 0: all gates, then all ups (gate_i at i, up_i at inter + i).

@@ -16,7 +16,10 @@
 //   delta_scan      per head, with a decay per key channel g = exp(-exp(A_h) softplus(a + bias)),
 //                   a write strength beta = sigmoid(b) and unit-length q (times dim^-1/2) and k:
 //                   S <- g * S (rows); u = beta (v - S^T k); S <- S + k u^T; o = S^T q
-//   gated_norm      per group of n outputs: o / sqrt(mean(o^2) + eps) * w * sigmoid(gate)
+//   gated_scan      per head, with a decay per key channel g = sigmoid(a + bias)^(1/tau) and q
+//                   times dim^-1/2: S <- g * S (rows) + k v^T; o = S^T q (gated linear attention)
+//   gated_norm      per group of n outputs: o / sqrt(mean(o^2) + eps) * w * f(gate), f the sigmoid
+//                   or SiLU
 #include "common.cuh"
 
 using namespace mrun;
@@ -178,6 +181,7 @@ causal_conv_vec_kernel(const TA* __restrict__ x, long ldx, const float* __restri
 // of the next tokens run under the walk over the present ones); a slice's rows start on a
 // 16-byte boundary, one bank group after the slice before, and are read four at a time.
 // ------------------------------------------------------------------------------------------
+constexpr int SCAN_HEAD_DECAY = 0, SCAN_DELTA = 1, SCAN_GATED = 2;      // which recurrence a scan runs
 constexpr int SCAN_WARPS = 4;
 constexpr int SCAN_ROWS = 16;       // key rows a lane holds at most
 
@@ -189,7 +193,8 @@ scan_prepare_kernel(const TA* __restrict__ q, const TA* __restrict__ k, const TA
                     const float* __restrict__ a, const TA* __restrict__ b, long ldb, const float* __restrict__ a_log,
                     const float* __restrict__ dt_bias, float* __restrict__ qf, float* __restrict__ kf,
                     float* __restrict__ gf, float* __restrict__ vf, float* __restrict__ bf, int G, int H, int D, int V,
-                    int delta, int silu_inputs) {
+                    int mode, int silu_inputs, float tau) {
+    const bool delta = mode == SCAN_DELTA;
     const size_t t = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int head = warp; head < G; head += 8) {
@@ -207,6 +212,8 @@ scan_prepare_kernel(const TA* __restrict__ q, const TA* __restrict__ k, const TA
             sq = warp_sum(sq); sk = warp_sum(sk);
             fq = (1.f / sqrtf((float)D)) / sqrtf(sq + 1e-6f);
             fk = 1.f / sqrtf(sk + 1e-6f);
+        } else if (mode == SCAN_GATED) {
+            fq = 1.f / sqrtf((float)D);
         }
         for (int i = lane; i < D; i += 32) {
             float qv = to_float(qr[i]), kv = to_float(kr[i]);
@@ -226,6 +233,9 @@ scan_prepare_kernel(const TA* __restrict__ q, const TA* __restrict__ k, const TA
             gf[t * H * D + e] = expf(-expf(a_log[e / D]) * step);
         }
         for (int e = tid; e < H; e += 256) bf[t * H + e] = 1.f / (1.f + expf(-to_float(b[t * ldb + e])));
+    } else if (mode == SCAN_GATED) {    // sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau)
+        for (int e = tid; e < H * D; e += 256)
+            gf[t * H * D + e] = expf(-softplus_f(-(a[t * H * D + e] + dt_bias[e])) / tau);
     }
 }
 
@@ -245,13 +255,14 @@ __device__ __forceinline__ void copy_async_16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 
-template <int R, bool DELTA, bool FULL>
+template <int R, int MODE, bool FULL>
 __global__ void __launch_bounds__(SCAN_WARPS * 32)
 scan_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const float* __restrict__ gf,
             const float* __restrict__ vf, const float* __restrict__ bf, const float* __restrict__ decay,
             float* __restrict__ state, float* __restrict__ out, const int* __restrict__ seg_q_start,
             const int* __restrict__ seg_slot, int group, int G, int H, int D, int V, int stage) {
     extern __shared__ __align__(16) float smem[];
+    constexpr bool DELTA = MODE == SCAN_DELTA, DECAYS = MODE != SCAN_HEAD_DECAY;     // DECAYS: a decay per key row
     constexpr int C = 32 / R, COLS = SCAN_WARPS * C, THREADS = SCAN_WARPS * 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int h = blockIdx.y, seg = blockIdx.z;
@@ -265,14 +276,14 @@ scan_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const fl
     const int mine = max(0, min(per, D - row0));
     const int ps = per + 4, Dp = R * ps;              // row i of a staged vector sits at (i / per) * ps + i % per
     const int kh = h / group;                         // the q/k head this head reads
-    const int vectors = DELTA ? 3 : 2;
+    const int vectors = DECAYS ? 3 : 2;
     const int buffer = stage * (vectors * Dp + COLS) + stage;         // floats of one buffer
 
     float S[SCAN_ROWS];
     float* st = state + (((size_t)seg_slot[seg] * H + h) * D) * V + col;
 #pragma unroll
     for (int i = 0; i < SCAN_ROWS; ++i) S[i] = (live && i < mine) ? st[(size_t)(row0 + i) * V] : 0.f;
-    const float head_decay = DELTA ? 0.f : decay[h];
+    const float head_decay = DECAYS ? 0.f : decay[h];
 
     auto fetch = [&](int which, int t0) {             // tokens t0 .. of the segment into buffer `which`
         const int m = min(stage, n - t0);
@@ -289,7 +300,7 @@ scan_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const fl
                 const int at = tt * Dp + (i / per) * ps + i % per;
                 copy_async_16(qs + at, qf + (row * G + kh) * D + i);
                 copy_async_16(ks + at, kf + (row * G + kh) * D + i);
-                if constexpr (DELTA) copy_async_16(gs + at, gf + (row * H + h) * D + i);
+                if constexpr (DECAYS) copy_async_16(gs + at, gf + (row * H + h) * D + i);
             }
         } else {
             for (int e = tid; e < m * D; e += THREADS) {
@@ -298,7 +309,7 @@ scan_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const fl
                 const int at = tt * Dp + (i / per) * ps + i % per;
                 copy_async_4(qs + at, qf + (row * G + kh) * D + i);
                 copy_async_4(ks + at, kf + (row * G + kh) * D + i);
-                if constexpr (DELTA) copy_async_4(gs + at, gf + (row * H + h) * D + i);
+                if constexpr (DECAYS) copy_async_4(gs + at, gf + (row * H + h) * D + i);
             }
         }
         for (int e = tid; e < m * COLS; e += THREADS) {
@@ -337,7 +348,7 @@ scan_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const fl
                     const float4 kv = k4[j], qv = q4[j];
                     kr[4 * j] = kv.x; kr[4 * j + 1] = kv.y; kr[4 * j + 2] = kv.z; kr[4 * j + 3] = kv.w;
                     qr[4 * j] = qv.x; qr[4 * j + 1] = qv.y; qr[4 * j + 2] = qv.z; qr[4 * j + 3] = qv.w;
-                    if constexpr (DELTA) {
+                    if constexpr (DECAYS) {
                         const float4 gv = g4[j];
                         gr[4 * j] = gv.x; gr[4 * j + 1] = gv.y; gr[4 * j + 2] = gv.z; gr[4 * j + 3] = gv.w;
                     }
@@ -353,6 +364,10 @@ scan_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const fl
 #pragma unroll
                 for (int i = 0; i < SCAN_ROWS; ++i)
                     if (FULL || i < mine) { S[i] = fmaf(kr[i], u, S[i]); o[i & 3] = fmaf(S[i], qr[i], o[i & 3]); }
+            } else if constexpr (MODE == SCAN_GATED) {
+#pragma unroll
+                for (int i = 0; i < SCAN_ROWS; ++i)
+                    if (FULL || i < mine) { S[i] = fmaf(gr[i], S[i], kr[i] * vv); o[i & 3] = fmaf(S[i], qr[i], o[i & 3]); }
             } else {
 #pragma unroll
                 for (int i = 0; i < SCAN_ROWS; ++i)
@@ -371,7 +386,7 @@ scan_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const fl
 template <typename TA>
 __global__ void __launch_bounds__(128)
 gated_norm_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_len, const TA* __restrict__ gate,
-                  long ldg, float eps, TA* __restrict__ out, long pairs, int groups, int n) {
+                  long ldg, float eps, TA* __restrict__ out, long pairs, int groups, int n, int gate_silu) {
     const long pair = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (pair >= pairs) return;
@@ -385,7 +400,7 @@ gated_norm_kernel(const float* __restrict__ o, const float* __restrict__ w, int 
     for (int i = lane; i < n; i += 32) {
         const int c = g * n + i;
         const float gv = to_float(gate[t * ldg + c]);
-        out[(t * groups + g) * n + i] = from_float<TA>(row[i] * inv * w[c % w_len] * (1.f / (1.f + expf(-gv))));
+        out[(t * groups + g) * n + i] = from_float<TA>(row[i] * inv * w[c % w_len] * ((gate_silu ? gv : 1.f) / (1.f + expf(-gv))));
     }
 }
 
@@ -395,7 +410,7 @@ gated_norm_kernel(const float* __restrict__ o, const float* __restrict__ w, int 
 template <typename TA>
 __global__ void __launch_bounds__(256)
 gated_norm_block_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_len, const TA* __restrict__ gate,
-                        long ldg, float eps, TA* __restrict__ out, int groups, int n) {
+                        long ldg, float eps, TA* __restrict__ out, int groups, int n, int gate_silu) {
     __shared__ float scratch[33];
     const long pair = blockIdx.x;
     const long t = pair / groups;
@@ -408,36 +423,37 @@ gated_norm_block_kernel(const float* __restrict__ o, const float* __restrict__ w
     for (int i = threadIdx.x; i < n; i += 256) {
         const int c = g * n + i;
         const float gv = to_float(gate[t * ldg + c]);
-        out[(t * groups + g) * n + i] = from_float<TA>(row[i] * inv * w[c % w_len] * (1.f / (1.f + expf(-gv))));
+        out[(t * groups + g) * n + i] = from_float<TA>(row[i] * inv * w[c % w_len] * ((gate_silu ? gv : 1.f) / (1.f + expf(-gv))));
     }
 }
 
-template <typename TA, bool DELTA>
+template <typename TA, int MODE>
 int launch_scan(const void* q, const void* k, const void* v, long ld, int group, const float* a, const void* b,
                 long ldb, const float* a_log, const float* dt_bias, const float* decay, float* state, float* out,
                 float* scratch, const int* seg_q_start, const int* seg_slot, int segments, int tokens, int H, int D,
-                int V, int silu_inputs, cudaStream_t stream) {
+                int V, int silu_inputs, float tau, cudaStream_t stream) {
+    constexpr bool DECAYS = MODE != SCAN_HEAD_DECAY;
     const int G = H / group;
     float* qf = scratch;
     float* kf = qf + (size_t)tokens * G * D;
     float* gf = kf + (size_t)tokens * G * D;          // the three that are copied 16 bytes at a time first
-    float* vf = gf + (DELTA ? (size_t)tokens * H * D : 0);
+    float* vf = gf + (DECAYS ? (size_t)tokens * H * D : 0);
     float* bf = vf + (size_t)tokens * H * V;
     scan_prepare_kernel<TA><<<tokens, 256, 0, stream>>>((const TA*)q, (const TA*)k, (const TA*)v, ld, a, (const TA*)b, ldb,
-                                                       a_log, dt_bias, qf, kf, gf, vf, bf, G, H, D, V, DELTA ? 1 : 0,
-                                                       silu_inputs);
+                                                       a_log, dt_bias, qf, kf, gf, vf, bf, G, H, D, V, MODE,
+                                                       silu_inputs, tau);
     const int R = D <= 16 ? 1 : D <= 32 ? 2 : D <= 64 ? 4 : D <= 128 ? 8 : 16;   // row slices: at most 16 rows a lane
     const int cols = SCAN_WARPS * (32 / R);
     const int per = (((D + R - 1) / R) + 3) & ~3;
     const int stage = D <= 128 ? 16 : 8;
     const dim3 grid((V + cols - 1) / cols, H, segments);
-    const size_t smem = sizeof(float) * 2 * ((size_t)stage * ((DELTA ? 3 : 2) * R * (per + 4) + cols) + stage);
+    const size_t smem = sizeof(float) * 2 * ((size_t)stage * ((DECAYS ? 3 : 2) * R * (per + 4) + cols) + stage);
 #define MRUN_SCAN_AS(SLICES, WHOLE)                                                                                 \
     do {                                                                                                           \
         if (smem > 48 * 1024)                                                                                      \
-            cudaFuncSetAttribute(scan_kernel<SLICES, DELTA, WHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+            cudaFuncSetAttribute(scan_kernel<SLICES, MODE, WHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
                                  (int)smem);                                                                       \
-        scan_kernel<SLICES, DELTA, WHOLE><<<grid, SCAN_WARPS * 32, smem, stream>>>(                                \
+        scan_kernel<SLICES, MODE, WHOLE><<<grid, SCAN_WARPS * 32, smem, stream>>>(                                 \
             qf, kf, gf, vf, bf, decay, state, out, seg_q_start, seg_slot, group, G, H, D, V, stage);               \
     } while (0)
 #define MRUN_SCAN(SLICES)                                                                                          \
@@ -515,11 +531,12 @@ MRUN_API int mrun_decay_scan(const void* q, const void* k, const void* v, long l
     MRUN_REQUIRE(H <= 65535 && segments <= 65535, "decay_scan: %d heads or %d segments exceed 65535", H, segments);
     if (segments == 0 || tokens == 0) return 0;
     if (act_dtype == MRUN_F32)
-        launch_scan<float, false>(q, k, v, ld, 1, nullptr, nullptr, 0, nullptr, nullptr, decay, state, out, scratch,
-                                  seg_q_start, seg_slot, segments, tokens, H, D, V, silu_inputs, stream);
+        launch_scan<float, SCAN_HEAD_DECAY>(q, k, v, ld, 1, nullptr, nullptr, 0, nullptr, nullptr, decay, state, out, scratch,
+                                            seg_q_start, seg_slot, segments, tokens, H, D, V, silu_inputs, 1.f, stream);
     else if (act_dtype == MRUN_BF16)
-        launch_scan<__nv_bfloat16, false>(q, k, v, ld, 1, nullptr, nullptr, 0, nullptr, nullptr, decay, state, out,
-                                          scratch, seg_q_start, seg_slot, segments, tokens, H, D, V, silu_inputs, stream);
+        launch_scan<__nv_bfloat16, SCAN_HEAD_DECAY>(q, k, v, ld, 1, nullptr, nullptr, 0, nullptr, nullptr, decay, state, out,
+                                                    scratch, seg_q_start, seg_slot, segments, tokens, H, D, V, silu_inputs,
+                                                    1.f, stream);
     else
         return mrun_set_error("decay_scan: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("decay_scan");
@@ -537,21 +554,44 @@ MRUN_API int mrun_delta_scan(const void* q, const void* k, const void* v, long l
     MRUN_REQUIRE(H <= 65535 && segments <= 65535, "delta_scan: %d heads or %d segments exceed 65535", H, segments);
     if (segments == 0 || tokens == 0) return 0;
     if (act_dtype == MRUN_F32)
-        launch_scan<float, true>(q, k, v, ld, group, a, b, ldb, a_log, dt_bias, nullptr, state, out, scratch,
-                                 seg_q_start, seg_slot, segments, tokens, H, D, V, 0, stream);
+        launch_scan<float, SCAN_DELTA>(q, k, v, ld, group, a, b, ldb, a_log, dt_bias, nullptr, state, out, scratch,
+                                       seg_q_start, seg_slot, segments, tokens, H, D, V, 0, 1.f, stream);
     else if (act_dtype == MRUN_BF16)
-        launch_scan<__nv_bfloat16, true>(q, k, v, ld, group, a, b, ldb, a_log, dt_bias, nullptr, state, out, scratch,
-                                         seg_q_start, seg_slot, segments, tokens, H, D, V, 0, stream);
+        launch_scan<__nv_bfloat16, SCAN_DELTA>(q, k, v, ld, group, a, b, ldb, a_log, dt_bias, nullptr, state, out, scratch,
+                                               seg_q_start, seg_slot, segments, tokens, H, D, V, 0, 1.f, stream);
     else
         return mrun_set_error("delta_scan: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("delta_scan");
     return 0;
 }
 
+// q, k: [H, D] a row (stride ld); v: [H, V] (stride ld); a: float32 [tokens, H * D], the decay
+// projection's output; bias: float32 [H * D]; the decay is sigmoid(a + bias)^(1 / tau).
+MRUN_API int mrun_gated_scan(const void* q, const void* k, const void* v, long ld, int act_dtype, const float* a,
+                             const float* bias, float tau, float* state, float* out, float* scratch,
+                             const int* seg_q_start, const int* seg_slot, int segments, int tokens, int H, int D, int V,
+                             cudaStream_t stream) {
+    MRUN_REQUIRE(H > 0 && D > 0 && V > 0 && segments >= 0 && tau > 0.f, "gated_scan: bad sizes");
+    MRUN_REQUIRE(D <= 256, "gated_scan: key size %d exceeds the supported 256", D);
+    MRUN_REQUIRE(H <= 65535 && segments <= 65535, "gated_scan: %d heads or %d segments exceed 65535", H, segments);
+    if (segments == 0 || tokens == 0) return 0;
+    if (act_dtype == MRUN_F32)
+        launch_scan<float, SCAN_GATED>(q, k, v, ld, 1, a, nullptr, 0, nullptr, bias, nullptr, state, out, scratch,
+                                       seg_q_start, seg_slot, segments, tokens, H, D, V, 0, tau, stream);
+    else if (act_dtype == MRUN_BF16)
+        launch_scan<__nv_bfloat16, SCAN_GATED>(q, k, v, ld, 1, a, nullptr, 0, nullptr, bias, nullptr, state, out, scratch,
+                                               seg_q_start, seg_slot, segments, tokens, H, D, V, 0, tau, stream);
+    else
+        return mrun_set_error("gated_scan: unknown dtype code %d", act_dtype);
+    MRUN_CHECK_LAUNCH("gated_scan");
+    return 0;
+}
+
 // o: float32 [tokens, groups * n]; w: float32 [w_len], element c of a row takes w[c % w_len];
-// gate: row t at gate + t * ldg; out: dense [tokens, groups * n].
+// gate: row t at gate + t * ldg; out: dense [tokens, groups * n].  gate_silu: the gate passes SiLU
+// instead of the sigmoid.
 MRUN_API int mrun_gated_norm(const float* o, const float* w, int w_len, const void* gate, long ldg, int act_dtype,
-                             float eps, void* out, int tokens, int groups, int n, cudaStream_t stream) {
+                             float eps, void* out, int tokens, int groups, int n, int gate_silu, cudaStream_t stream) {
     MRUN_REQUIRE(tokens >= 0 && groups > 0 && n > 0 && w_len > 0, "gated_norm: bad sizes");
     MRUN_REQUIRE(ldg >= (long)groups * n, "gated_norm: the gate's row stride %ld is below the row", ldg);
     if (tokens == 0) return 0;
@@ -560,10 +600,10 @@ MRUN_API int mrun_gated_norm(const float* o, const float* w, int w_len, const vo
     if (n >= 1024) {            // a block a pair
         if (act_dtype == MRUN_F32)
             gated_norm_block_kernel<float><<<(unsigned)pairs, 256, 0, stream>>>(o, w, w_len, (const float*)gate, ldg, eps,
-                                                                                 (float*)out, groups, n);
+                                                                                 (float*)out, groups, n, gate_silu);
         else if (act_dtype == MRUN_BF16)
             gated_norm_block_kernel<__nv_bfloat16><<<(unsigned)pairs, 256, 0, stream>>>(
-                o, w, w_len, (const __nv_bfloat16*)gate, ldg, eps, (__nv_bfloat16*)out, groups, n);
+                o, w, w_len, (const __nv_bfloat16*)gate, ldg, eps, (__nv_bfloat16*)out, groups, n, gate_silu);
         else
             return mrun_set_error("gated_norm: unknown dtype code %d", act_dtype);
         MRUN_CHECK_LAUNCH("gated_norm");
@@ -571,10 +611,10 @@ MRUN_API int mrun_gated_norm(const float* o, const float* w, int w_len, const vo
     }
     if (act_dtype == MRUN_F32)
         gated_norm_kernel<float><<<blocks, 128, 0, stream>>>(o, w, w_len, (const float*)gate, ldg, eps, (float*)out,
-                                                              pairs, groups, n);
+                                                              pairs, groups, n, gate_silu);
     else if (act_dtype == MRUN_BF16)
         gated_norm_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, w, w_len, (const __nv_bfloat16*)gate, ldg, eps,
-                                                                      (__nv_bfloat16*)out, pairs, groups, n);
+                                                                      (__nv_bfloat16*)out, pairs, groups, n, gate_silu);
     else
         return mrun_set_error("gated_norm: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("gated_norm");

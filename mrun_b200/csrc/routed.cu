@@ -16,6 +16,14 @@
 //                 u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1), times the
 //                 token's weight of the block's expert or the row's weight
 //
+// And the choice of a router with sigmoid scores and groups of experts:
+//
+//   route_grouped the experts form equal groups of neighbours; a group's score is the sum of its
+//                 group_top largest scores; only experts of the keep best groups can be chosen;
+//                 the top allowed experts with the largest scores weigh score / (sum + 1e-20) *
+//                 scale; one more logit column, if there is one, becomes the sigmoid weight of a
+//                 shared expert
+//
 // Inside an expert's range the rows stand in the order in which the pairs arrived (an atomic
 // counter); a row's result does not depend on where in the range it stands, and the combine adds
 // a token's rows in a fixed order, so the output has the same bits every run.
@@ -147,40 +155,135 @@ __global__ void table_route_kernel(const int* __restrict__ ids, const int* __res
     }
 }
 
-// u: [rows, blocks * 2 * ff]; act: [rows, blocks * ff].  weights: per (row, block) when
-// per_block, else one per row, or null.
+// A warp a token.  logits: row t at logits + t * ldz, experts columns and then `extra` (0 or 1)
+// more.  weights: dense [tokens, experts]; shared_w: [tokens] or null; chosen: [tokens, top] or
+// null.  Ties go to the lower index.  Shared memory: experts + groups floats a warp.
+__global__ void __launch_bounds__(128)
+route_grouped_kernel(const float* __restrict__ logits, long ldz, float* __restrict__ weights,
+                     float* __restrict__ shared_w, int* __restrict__ chosen, int tokens, int experts, int top,
+                     int groups, int keep, int group_top, float scale) {
+    extern __shared__ float route_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= tokens) return;
+    float* s = route_smem + (size_t)warp * (experts + groups);
+    float* gs = s + experts;
+    const float* z = logits + (size_t)t * ldz;
+    for (int e = lane; e < experts; e += 32) {
+        s[e] = 1.f / (1.f + expf(-z[e]));
+        weights[(size_t)t * experts + e] = 0.f;
+    }
+    if (shared_w && lane == 0) shared_w[t] = 1.f / (1.f + expf(-z[experts]));
+    __syncwarp();
+    const int size = experts / groups;
+    if (groups > 1) {
+        // a group's score: its group_top largest scores, found one after the other in the order
+        // (larger score, then lower index)
+        for (int g = lane; g < groups; g += 32) {
+            float sum = 0.f, last = INFINITY;
+            int last_i = -1;
+            for (int k = 0; k < group_top && k < size; ++k) {
+                float best = -1.f;
+                int best_i = size;
+                for (int i = 0; i < size; ++i) {
+                    const float v = s[g * size + i];
+                    const bool after = v < last || (v == last && i > last_i);
+                    if (after && (v > best || (v == best && i < best_i))) { best = v; best_i = i; }
+                }
+                sum += best; last = best; last_i = best_i;
+            }
+            gs[g] = sum;
+        }
+        __syncwarp();
+        // the keep best groups stay; the scores of the others leave the choice
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY;
+            int best_g = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32)
+                if (gs[g] > best || (gs[g] == best && g < best_g)) { best = gs[g]; best_g = g; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+                if (ob > best || (ob == best && og < best_g)) { best = ob; best_g = og; }
+            }
+            __syncwarp();
+            if (lane == 0) gs[best_g] = -INFINITY;      // marks a group that stays
+            __syncwarp();
+        }
+        for (int e = lane; e < experts; e += 32)
+            if (gs[e / size] != -INFINITY) s[e] = -1.f;
+        __syncwarp();
+    }
+    float total = 0.f, mine = 0.f;       // lane k keeps the score of the k-th choice
+    int mine_e = -1;
+    for (int k = 0; k < top; ++k) {
+        float best = -1.f;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32)
+            if (s[e] > best || (s[e] == best && e < best_e)) { best = s[e]; best_e = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        __syncwarp();
+        if (lane == 0) s[best_e] = -2.f;
+        __syncwarp();
+        total += best;
+        if (chosen && lane == 0) chosen[(size_t)t * top + k] = best_e;
+        if (k == lane) { mine = best; mine_e = best_e; }
+    }
+    // the weights need the total of all choices: lane k kept the k-th choice (chosen experts
+    // stand as -2 in s)
+    const float norm = scale / (total + 1e-20f);
+    if (top <= 32) {
+        if (lane < top) weights[(size_t)t * experts + mine_e] = mine * norm;
+    } else {
+        // more than 32 choices: recompute every chosen expert's score from its logit
+        for (int e = lane; e < experts; e += 32)
+            if (s[e] == -2.f) weights[(size_t)t * experts + e] = (1.f / (1.f + expf(-z[e]))) * norm;
+    }
+}
+
+// u: row r at u + r * ldu, blocks * 2 * ff columns; act: row r at act + r * lda, blocks * ff
+// columns.  weights: per (row, block) when per_block (row r at weights + r * ldw), else one per row
+// (at weights + r * ldw), or null.
 template <typename TA, bool EXACT>
-__global__ void clamped_glu_kernel(const TA* __restrict__ u, TA* __restrict__ act, const float* __restrict__ weights,
-                                   int per_block, long total, int blocks, int ff, float limit, float alpha) {
+__global__ void clamped_glu_kernel(const TA* __restrict__ u, long ldu, TA* __restrict__ act, long lda,
+                                   const float* __restrict__ weights, long ldw, int per_block, long total, int blocks,
+                                   int ff, float limit, float alpha, float up_offset) {
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long row = i / ((long)blocks * ff);
     const int c = (int)(i - row * blocks * ff);
     const int e = c / ff, j = c - e * ff;
-    const TA* base = u + (row * blocks + e) * 2 * ff;
+    const TA* base = u + row * ldu + (size_t)e * 2 * ff;
     const float g = fminf(to_float(base[j]), limit);
     const float up = fminf(fmaxf(to_float(base[ff + j]), -limit), limit);
-    const float w = weights ? (per_block ? weights[row * blocks + e] : weights[row]) : 1.f;
+    const float w = weights ? (per_block ? weights[row * ldw + e] : weights[row * ldw]) : 1.f;
     float s;
     if constexpr (EXACT) s = 1.f / (1.f + expf(-alpha * g));
     else s = __fdividef(1.f, 1.f + __expf(-alpha * g));
-    act[i] = from_float<TA>(g * s * (up + 1.f) * w);
+    act[row * lda + c] = from_float<TA>(g * s * (up + up_offset) * w);
 }
 
 // Eight outputs a thread (ff a multiple of 8, 16-byte aligned rows): grid.x walks the rows, grid.y the chunks.
 template <typename TA, bool EXACT>
 __global__ void __launch_bounds__(256)
-clamped_glu_vec_kernel(const TA* __restrict__ u, TA* __restrict__ act, const float* __restrict__ weights, int per_block,
-                       int blocks, int ff, float limit, float alpha) {
+clamped_glu_vec_kernel(const TA* __restrict__ u, long ldu, TA* __restrict__ act, long lda,
+                       const float* __restrict__ weights, long ldw, int per_block, int blocks, int ff, float limit,
+                       float alpha, float up_offset) {
     const long row = blockIdx.x;
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
     if (c >= blocks * ff) return;
     const int e = c / ff, j = c - e * ff;
-    const TA* base = u + (row * blocks + e) * 2 * ff;
+    const TA* base = u + row * ldu + (size_t)e * 2 * ff;
     float g[8], up[8];
     Vec8<TA>::load(base + j, g);
     Vec8<TA>::load(base + ff + j, up);
-    const float w = weights ? (per_block ? weights[row * blocks + e] : weights[row]) : 1.f;
+    const float w = weights ? (per_block ? weights[row * ldw + e] : weights[row * ldw]) : 1.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const float gv = fminf(g[i], limit);
@@ -188,9 +291,9 @@ clamped_glu_vec_kernel(const TA* __restrict__ u, TA* __restrict__ act, const flo
         float s;
         if constexpr (EXACT) s = 1.f / (1.f + expf(-alpha * gv));
         else s = __fdividef(1.f, 1.f + __expf(-alpha * gv));
-        g[i] = gv * s * (uv + 1.f) * w;
+        g[i] = gv * s * (uv + up_offset) * w;
     }
-    Vec8<TA>::store(act + row * blocks * ff + c, g);
+    Vec8<TA>::store(act + row * lda + c, g);
 }
 
 }  // namespace
@@ -205,32 +308,56 @@ MRUN_API int mrun_table_route(const int* ids, const int* table, float* weights, 
     return 0;
 }
 
-MRUN_API int mrun_clamped_glu(const void* u, void* act, int act_dtype, const float* weights, int per_block, int rows,
-                              int blocks, int ff, float limit, float alpha, cudaStream_t stream) {
+MRUN_API int mrun_route_grouped(const float* logits, long ldz, float* weights, float* shared_w, int* chosen, int tokens,
+                                int experts, int top, int groups, int keep, int group_top, float scale,
+                                cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && groups > 0 && keep > 0 && group_top > 0,
+                 "route_grouped: bad sizes tokens=%d experts=%d top=%d groups=%d", tokens, experts, top, groups);
+    MRUN_REQUIRE(experts % groups == 0 && keep <= groups && top <= keep * (experts / groups),
+                 "route_grouped: %d experts in %d groups of which %d stay cannot give %d choices", experts, groups, keep, top);
+    MRUN_REQUIRE(experts + groups <= 2048, "route_grouped: %d experts exceed the supported 2048", experts + groups);
+    MRUN_REQUIRE(ldz >= experts + (shared_w ? 1 : 0), "route_grouped: the logits' row stride is below the row");
+    if (tokens == 0) return 0;
+    const size_t smem = 4 * (size_t)(experts + groups) * sizeof(float);
+    route_grouped_kernel<<<(tokens + 3) / 4, 128, smem, stream>>>(logits, ldz, weights, shared_w, chosen, tokens, experts,
+                                                                top, groups, keep, group_top, scale);
+    MRUN_CHECK_LAUNCH("route_grouped");
+    return 0;
+}
+
+// limit: the clamp of gate and up (infinity: none); up_offset: what is added to up before the product.
+MRUN_API int mrun_clamped_glu(const void* u, long ldu, void* act, long lda, int act_dtype, const float* weights, long ldw,
+                              int per_block, int rows, int blocks, int ff, float limit, float alpha, float up_offset,
+                              cudaStream_t stream) {
     MRUN_REQUIRE(rows >= 0 && blocks > 0 && ff > 0, "clamped_glu: bad sizes rows=%d blocks=%d ff=%d", rows, blocks, ff);
+    MRUN_REQUIRE(ldu >= (long)blocks * 2 * ff && lda >= (long)blocks * ff, "clamped_glu: a row stride below the row");
     if (rows == 0) return 0;
     const long total = (long)rows * blocks * ff;
     const unsigned grid = (unsigned)((total + 255) / 256);
-    if (ff % 8 == 0 && ((((uintptr_t)u) | ((uintptr_t)act)) & 15) == 0 && rows <= 0x7fffffff) {
+    const size_t unit = act_dtype == MRUN_F32 ? 4 : 2;
+    if (ff % 8 == 0 && ((((uintptr_t)u) | ((uintptr_t)act)) & 15) == 0 && (ldu * unit) % 16 == 0 && (lda * unit) % 16 == 0 &&
+        rows <= 0x7fffffff) {
         const dim3 vec_grid(rows, (blocks * ff / 8 + 255) / 256);
         if (act_dtype == MRUN_F32)
-            clamped_glu_vec_kernel<float, true><<<vec_grid, 256, 0, stream>>>((const float*)u, (float*)act, weights,
-                                                                               per_block, blocks, ff, limit, alpha);
+            clamped_glu_vec_kernel<float, true><<<vec_grid, 256, 0, stream>>>((const float*)u, ldu, (float*)act, lda, weights,
+                                                                               ldw, per_block, blocks, ff, limit, alpha,
+                                                                               up_offset);
         else if (act_dtype == MRUN_BF16)
             clamped_glu_vec_kernel<__nv_bfloat16, false><<<vec_grid, 256, 0, stream>>>(
-                (const __nv_bfloat16*)u, (__nv_bfloat16*)act, weights, per_block, blocks, ff, limit, alpha);
+                (const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)act, lda, weights, ldw, per_block, blocks, ff, limit, alpha,
+                up_offset);
         else
             return mrun_set_error("clamped_glu: unknown dtype code %d", act_dtype);
         MRUN_CHECK_LAUNCH("clamped_glu");
         return 0;
     }
     if (act_dtype == MRUN_F32)
-        clamped_glu_kernel<float, true><<<grid, 256, 0, stream>>>((const float*)u, (float*)act, weights, per_block, total,
-                                                                   blocks, ff, limit, alpha);
+        clamped_glu_kernel<float, true><<<grid, 256, 0, stream>>>((const float*)u, ldu, (float*)act, lda, weights, ldw,
+                                                                   per_block, total, blocks, ff, limit, alpha, up_offset);
     else if (act_dtype == MRUN_BF16)
-        clamped_glu_kernel<__nv_bfloat16, false><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)u, (__nv_bfloat16*)act,
-                                                                            weights, per_block, total, blocks, ff, limit,
-                                                                            alpha);
+        clamped_glu_kernel<__nv_bfloat16, false><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)act,
+                                                                            lda, weights, ldw, per_block, total, blocks, ff,
+                                                                            limit, alpha, up_offset);
     else
         return mrun_set_error("clamped_glu: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("clamped_glu");

@@ -14,6 +14,8 @@
 //
 // Kernels:
 //   embed_streams   the embedding row of a token copied into each of its S streams
+//   embed_bigram    the same with the row times a scale plus a row of a second table, chosen by a
+//                   hash of the token and the one before it (the request's state across steps)
 //   streams_step    pending write + read + RMS norm (eps inside the root), see above
 #include "common.cuh"
 
@@ -34,6 +36,50 @@ __global__ void embed_streams_kernel(const TW* __restrict__ table, const int* __
     for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
         const float v = ok ? to_float(row[h]) : 0.f;
         for (int s = 0; s < copies; ++s) dst[(size_t)s * hidden + h] = v;
+    }
+}
+
+// The row of the pair table for every token: a hash of the token and the one before it in its
+// request, the table's last row for a request's first token, -1 for a padding row.  The token
+// before a step's first token of a request is the request's state.  A token is the first of its
+// segment when the row before it belongs to another request or is not the position before.
+__global__ void bigram_rows_kernel(const int* __restrict__ ids, const int* __restrict__ positions,
+                                   const int* __restrict__ token_slot, const int* __restrict__ state,
+                                   int* __restrict__ rows, int tokens, int vocab, int buckets, long long mul_prev,
+                                   long long mul_cur) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens) return;
+    const int pos = positions[t], id = ids[t];
+    if (pos < 0 || id < 0 || id >= vocab) { rows[t] = -1; return; }
+    if (pos == 0) { rows[t] = buckets; return; }
+    const bool first = t == 0 || token_slot[t - 1] != token_slot[t] || positions[t - 1] != pos - 1;
+    const int before = first ? state[token_slot[t]] : ids[t - 1];
+    rows[t] = (int)(((long long)before * mul_prev + (long long)id * mul_cur) % (long long)buckets);
+}
+
+// out[t, s] = table[ids[t]] * scale + pairs[rows[t]] for each of the S streams; the block of a
+// request's last token of the step leaves that token as the request's state.
+template <typename TW>
+__global__ void embed_bigram_kernel(const TW* __restrict__ table, const TW* __restrict__ pairs,
+                                    const int* __restrict__ ids, const int* __restrict__ positions,
+                                    const int* __restrict__ token_slot, const int* __restrict__ rows,
+                                    int* __restrict__ state, float* __restrict__ out, int tokens, int hidden, int vocab,
+                                    int copies, float scale) {
+    const int t = blockIdx.x;
+    const int id = ids[t], pos = positions[t];
+    const bool ok = pos >= 0 && id >= 0 && id < vocab;
+    const TW* row = table + (size_t)(ok ? id : 0) * hidden;
+    const int pair = (pairs && ok) ? rows[t] : -1;
+    const TW* add = pair >= 0 ? pairs + (size_t)pair * hidden : nullptr;
+    float* dst = out + (size_t)t * copies * hidden;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        float v = ok ? to_float(row[h]) * scale : 0.f;
+        if (add) v += to_float(add[h]);
+        for (int s = 0; s < copies; ++s) dst[(size_t)s * hidden + h] = v;
+    }
+    if (state && ok && threadIdx.x == 0) {
+        const bool last = t == tokens - 1 || token_slot[t + 1] != token_slot[t] || positions[t + 1] != pos + 1;
+        if (last) state[token_slot[t]] = id;
     }
 }
 
@@ -184,6 +230,36 @@ MRUN_API int mrun_embed_streams(const void* table, int table_dtype, const int* i
     else
         return mrun_set_error("embed_streams: unknown dtype code %d", table_dtype);
     MRUN_CHECK_LAUNCH("embed_streams");
+    return 0;
+}
+
+// table: [vocab, hidden]; pairs: [buckets + 1, hidden] in the same dtype, or null (no second
+// table); state: int32 [slots], the last token each request brought; rows: int32 [tokens] scratch.
+MRUN_API int mrun_embed_bigram(const void* table, const void* pairs, int table_dtype, const int* ids,
+                               const int* positions, const int* token_slot, int* state, int* rows, float* out,
+                               int tokens, int hidden, int vocab, int copies, float scale, int buckets, long mul_prev,
+                               long mul_cur, cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0 && copies >= 1,
+                 "embed_bigram: bad sizes tokens=%d hidden=%d vocab=%d copies=%d", tokens, hidden, vocab, copies);
+    MRUN_REQUIRE(pairs == nullptr || (buckets > 0 && state != nullptr && rows != nullptr && mul_prev >= 0 && mul_cur >= 0),
+                 "embed_bigram: a pair table needs buckets, multipliers, a state and scratch rows");
+    if (tokens == 0) return 0;
+    if (pairs) {
+        bigram_rows_kernel<<<(tokens + 127) / 128, 128, 0, stream>>>(ids, positions, token_slot, state, rows, tokens,
+                                                                     vocab, buckets, mul_prev, mul_cur);
+        MRUN_CHECK_LAUNCH("embed_bigram (rows)");
+    }
+    if (table_dtype == MRUN_F32)
+        embed_bigram_kernel<float><<<tokens, 256, 0, stream>>>((const float*)table, (const float*)pairs, ids, positions,
+                                                                token_slot, rows, pairs ? state : nullptr, out, tokens,
+                                                                hidden, vocab, copies, scale);
+    else if (table_dtype == MRUN_BF16)
+        embed_bigram_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
+            (const __nv_bfloat16*)table, (const __nv_bfloat16*)pairs, ids, positions, token_slot, rows,
+            pairs ? state : nullptr, out, tokens, hidden, vocab, copies, scale);
+    else
+        return mrun_set_error("embed_bigram: unknown dtype code %d", table_dtype);
+    MRUN_CHECK_LAUNCH("embed_bigram");
     return 0;
 }
 

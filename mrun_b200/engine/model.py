@@ -13,7 +13,7 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..kernels import ops
-from ..parts import ARRANGEMENTS, NORMS, TRANSFORMS, Runtime
+from ..parts import ARRANGEMENTS, EMBEDDINGS, NORMS, TRANSFORMS, Runtime
 from ..parts.base import local
 from .batch import StepContext
 
@@ -28,6 +28,16 @@ class Model:
         self.embedding = runtime.matrix(tensors[spec.embedding_name])
         if self.embedding.shape != (spec.vocab_size, spec.hidden_size):
             raise ValueError("the embedding table does not have the spec's shape")
+        # an embedding part in place of the plain lookup: it gets the token table (as the model
+        # holds it) under the empty name and its other tensors by their own names
+        self.embedder = None
+        if spec.embedding is not None:
+            if spec.tie_embeddings:
+                raise ValueError("an embedding part does not share its table with the output head")
+            mine = {t.name: tensors[t.name] for t in EMBEDDINGS.tensor_specs(spec.embedding, spec.embedding_name)
+                    if t.name in tensors and t.name != spec.embedding_name}
+            mine[""] = self.embedding
+            self.embedder = EMBEDDINGS.build(spec.embedding, mine, runtime)
         self.head = self.embedding if spec.tie_embeddings else runtime.matrix(tensors[spec.head_name])
         self.blocks = [ARRANGEMENTS.get(layer.arrangement)(layer, tensors, runtime) for layer in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, local(tensors, spec.final_norm_prefix), runtime)
@@ -49,10 +59,12 @@ class Model:
             # a block that keeps state of its own (an input convolution) states the need itself
             owner = block if hasattr(block, "cache_need") else block.mixer
             needs.append(None if entry.cache_of is not None else owner.cache_need())
+        if self.embedder is not None:       # the embedding part's state comes after the schedule's entries
+            needs.append(self.embedder.cache_need())
         return needs
 
     def cache_shares(self) -> List[Optional[int]]:
-        return [entry.cache_of for entry in self.order]
+        return [entry.cache_of for entry in self.order] + ([None] if self.embedder is not None else [])
 
     def activation_elements(self) -> int:
         """The widest set of per-token temporaries any part declares (parts without the hint
@@ -67,7 +79,8 @@ class Model:
 
     @property
     def graph_safe(self) -> bool:
-        return all(getattr(block.mixer, "graph_safe", False) for block in self.blocks)
+        return (all(getattr(block.mixer, "graph_safe", False) for block in self.blocks)
+                and (self.embedder is None or getattr(self.embedder, "graph_safe", False)))
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
@@ -90,6 +103,8 @@ class Model:
             walk(block)
         for t in (self.embedding, self.head):
             walk(t)
+        if self.embedder is not None:
+            walk(self.embedder)
         return total
 
     # ------------------------------------------------------------------ forward
@@ -98,7 +113,9 @@ class Model:
         ops.RowSums.begin_step(self.runtime.device)
         resid = torch.empty((ctx.num_tokens, self.spec.streams * self.spec.hidden_size), dtype=torch.float32,
                             device=self.runtime.device)
-        if self.spec.streams > 1:           # every stream starts as the embedding's row
+        if self.embedder is not None:
+            self.embedder.forward(ctx, caches[len(self.order)], resid, self.spec.streams)
+        elif self.spec.streams > 1:         # every stream starts as the embedding's row
             ops.embed_streams(self.embedding, ctx.token_ids, resid, self.spec.streams)
         else:
             ops.embed(self.embedding, ctx.token_ids, resid)

@@ -123,13 +123,54 @@ def qk_norm_rope_cache(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: i
                      _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _stream())
 
 
+def proj_norm_rope_cache(x: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, kv_heads: int, dim: int,
+                         vdim: int, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                         rot: Optional[torch.Tensor], rotary_dim: int, pairing: str, slots: Optional[torch.Tensor],
+                         k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], page_size: int) -> None:
+    """RMS norm of q and of k over the whole projection (all heads of a token together, weights of
+    that size), rotation of the first ``rotary_dim`` features of every head, k and v into the
+    pages ``slots`` names (key pages [pages, kv_heads, page, dim], value pages [.., vdim]).  ``x``:
+    rows whose q, k and v heads start at columns ``q_off``, ``k_off``, ``v_off``; q is worked on in
+    place.  ``k_off`` < 0: the rows have no keys and values."""
+    ld = _strided_rows(x, "x")
+    tokens = x.shape[0]
+    for name, w, n in (("q_weight", q_weight, heads * dim), ("k_weight", k_weight, kv_heads * dim)):
+        if w is not None:
+            _check(w, name, torch.float32)
+            if w.numel() != n:
+                raise KernelError(f"proj_norm_rope_cache: {name} has {w.numel()} elements, the projection has {n}")
+    if rot is not None:
+        _check(rot, "rot", torch.float32)
+        if rot.shape != (tokens, rotary_dim // 2, 2):
+            raise KernelError(f"proj_norm_rope_cache: rot is {tuple(rot.shape)}, expected {(tokens, rotary_dim // 2, 2)}")
+    if k_off >= 0 and slots is not None:
+        _check(slots, "slots", torch.int32)
+        for name, c, n in (("k_cache", k_cache, dim), ("v_cache", v_cache, vdim)):
+            _check(c, name, x.dtype)
+            if c.dim() != 4 or c.shape[1:] != (kv_heads, page_size, n):
+                raise KernelError(f"proj_norm_rope_cache: {name} is {tuple(c.shape)}, expected "
+                                  f"[pages, {kv_heads}, {page_size}, {n}]")
+    width = x.shape[1]
+    if q_off + heads * dim > width or (k_off >= 0 and (k_off + kv_heads * dim > width or v_off + kv_heads * vdim > width)):
+        raise KernelError("proj_norm_rope_cache: the heads do not fit the rows")
+    _lib.core().call("mrun_proj_norm_rope_cache", _ptr(x), _c_long(ld), _c_long(q_off), _c_long(k_off), _c_long(v_off),
+                     dtype_code(x.dtype), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(rot),
+                     _c_int(rotary_dim if rot is not None else 0), _c_int(PAIRINGS[pairing]),
+                     _ptr(slots if k_off >= 0 else None), _ptr(k_cache), _ptr(v_cache), _c_int(tokens), _c_int(heads),
+                     _c_int(kv_heads), _c_int(dim), _c_int(vdim), _c_int(page_size), _stream())
+
+
 def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor,
                             v_cache: torch.Tensor, block_tables: torch.Tensor, token_slot: torch.Tensor,
-                            positions: torch.Tensor, heads: int, scale: float, window: int = 0) -> torch.Tensor:
+                            positions: torch.Tensor, heads: int, scale: float, window: int = 0, sink: bool = False,
+                            gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of every token over its request's pages, 32-bit arithmetic on CUDA cores.
 
     ``q`` may be a view into a wider buffer: row t starts ``q_stride`` elements after row t-1.
     ``block_tables`` has one row per state slot; ``token_slot[t]`` names the row of token t.
+    The value pages may have another feature size than the key pages.  ``sink``: one more term of
+    score 0 without a value in the softmax's denominator.  ``gate``: [tokens, heads] in q's dtype
+    (rows may be strided), whose sigmoid multiplies each head's output.
     """
     _check(q, "q", dense=False); _check(out, "out", q.dtype)
     _check(k_cache, "k_cache", q.dtype); _check(v_cache, "v_cache", q.dtype)
@@ -137,18 +178,24 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
     _check(positions, "positions", torch.int32)
     pages, kv_heads, page_size, head_dim = k_cache.shape
     tokens = positions.numel()
-    if v_cache.shape != k_cache.shape:
-        raise KernelError("paged_attention: k and v caches differ in shape")
-    if out.shape != (tokens, heads * head_dim) or token_slot.numel() != tokens:
+    if v_cache.dim() != 4 or v_cache.shape[:3] != k_cache.shape[:3]:
+        raise KernelError("paged_attention: k and v caches differ in pages, heads or page size")
+    value_dim = v_cache.shape[3]
+    if out.shape != (tokens, heads * value_dim) or token_slot.numel() != tokens:
         raise KernelError(f"paged_attention: out {tuple(out.shape)} / token_slot {token_slot.numel()} "
-                          f"do not match {tokens} tokens of {heads}x{head_dim}")
+                          f"do not match {tokens} tokens of {heads}x{value_dim}")
     if block_tables.dim() != 2:
         raise KernelError("paged_attention: block_tables must be [slots, max_blocks]")
+    gate_stride = 0
+    if gate is not None:
+        gate_stride = _strided_rows(gate, "gate")
+        if gate.shape != (tokens, heads) or gate.dtype != q.dtype:
+            raise KernelError(f"paged_attention: gate is {tuple(gate.shape)} {gate.dtype}, expected {(tokens, heads)} {q.dtype}")
     _lib.core().call("mrun_paged_attention_generic", _ptr(q), _c_long(q_stride), _ptr(out), _ptr(k_cache),
                      _ptr(v_cache), dtype_code(q.dtype), _ptr(block_tables), _c_int(block_tables.shape[1]),
                      _ptr(token_slot), _ptr(positions), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
-                     _c_int(head_dim), _c_int(page_size), _c_long(pages * kv_heads * page_size),
-                     _c_float(scale), _c_int(window), _stream())
+                     _c_int(head_dim), _c_int(value_dim), _c_int(page_size), _c_long(pages * kv_heads * page_size),
+                     _c_float(scale), _c_int(window), _c_int(1 if sink else 0), _ptr(gate), _c_long(gate_stride), _stream())
     return out
 
 
@@ -824,6 +871,31 @@ def embed_streams(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, cop
     return out
 
 
+def embed_bigram(table: torch.Tensor, pairs: Optional[torch.Tensor], ids: torch.Tensor, positions: torch.Tensor,
+                 token_slot: torch.Tensor, state: Optional[torch.Tensor], out: torch.Tensor, copies: int, scale: float,
+                 buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """out[t, s] = table[ids[t]] * scale + pairs[row(t)] for each of the ``copies`` streams; row(t)
+    = (previous token * mul_prev + token * mul_cur) mod buckets, row ``buckets`` at position 0.
+    ``state`` (int32 [slots, 1]) holds the last token every request brought and is left up to
+    date.  ``pairs`` None: the scaled row alone.  Padding rows (negative position) become zero."""
+    _check(table, "table"); _check(ids, "ids", torch.int32); _check(out, "out", torch.float32)
+    _check(positions, "positions", torch.int32); _check(token_slot, "token_slot", torch.int32)
+    vocab, hidden = table.shape
+    tokens = ids.numel()
+    if out.shape != (tokens, copies * hidden):
+        raise KernelError(f"embed_bigram: out is {tuple(out.shape)}, expected {(tokens, copies * hidden)}")
+    rows = None
+    if pairs is not None:
+        _check(pairs, "pairs", table.dtype); _check(state, "state", torch.int32)
+        if pairs.shape != (buckets + 1, hidden):
+            raise KernelError(f"embed_bigram: pairs is {tuple(pairs.shape)}, expected {(buckets + 1, hidden)}")
+        rows = torch.empty(tokens, dtype=torch.int32, device=ids.device)
+    _lib.core().call("mrun_embed_bigram", _ptr(table), _ptr(pairs), dtype_code(table.dtype), _ptr(ids), _ptr(positions),
+                     _ptr(token_slot), _ptr(state), _ptr(rows), _ptr(out), _c_int(tokens), _c_int(hidden), _c_int(vocab),
+                     _c_int(copies), _c_float(scale), _c_int(buckets), _c_long(mul_prev), _c_long(mul_cur), _stream())
+    return out
+
+
 class PendingStreams:
     """A sublayer's output (float32 rows) that has not been written into the token's streams yet,
     with the coefficients of the write: x_t <- sum_s mix[s, t] x_s + out[t] * y (``mix`` and
@@ -954,10 +1026,36 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tenso
     return out
 
 
+def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, bias: torch.Tensor, tau: float,
+               state: torch.Tensor, ctx, heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """Linear attention with a decay per head and key channel over each request's tokens: g =
+    sigmoid(a + bias)^(1 / tau), S <- g * S (rows) + k v^T, o = S^T (q * dim^-1/2), from and into
+    ``state`` (float32 [slots, heads, dim, vdim]).  q, k ([tokens, heads * dim]) and v ([tokens,
+    heads * vdim]): column slices of one matrix; ``a``: float32 [tokens, heads * dim]; ``bias``:
+    float32 [heads * dim].  Returns float32 [tokens, heads * vdim]."""
+    ld = _strided_rows(q, "q")
+    if _strided_rows(k, "k") != ld or _strided_rows(v, "v") != ld or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise KernelError("gated_scan: q, k and v must be slices of one matrix")
+    _check(a, "a", torch.float32); _check(bias, "bias", torch.float32); _check(state, "state", torch.float32)
+    tokens = q.shape[0]
+    if q.shape[1] != heads * dim or k.shape[1] != heads * dim or v.shape[1] != heads * vdim \
+            or a.shape != (tokens, heads * dim) or bias.numel() != heads * dim or state.shape[1:] != (heads, dim, vdim):
+        raise KernelError("gated_scan: sizes do not match")
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=q.device)
+    scratch = torch.empty(tokens * heads * (3 * dim + vdim), dtype=torch.float32, device=q.device)
+    _lib.core().call("mrun_gated_scan", _ptr(q), _ptr(k), _ptr(v), _c_long(ld), dtype_code(q.dtype), _ptr(a), _ptr(bias),
+                     _c_float(tau), _ptr(state), _ptr(out), _ptr(scratch), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot),
+                     _c_int(ctx.num_segments), _c_int(tokens), _c_int(heads), _c_int(dim), _c_int(vdim), _stream())
+    return out
+
+
+GATE_SHAPES = {"sigmoid": 0, "silu": 1}        # what a gated norm passes its gate through
+
+
 def gated_norm(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float, groups: int,
-               out_dtype: torch.dtype) -> torch.Tensor:
+               out_dtype: torch.dtype, gate_function: str = "sigmoid") -> torch.Tensor:
     """Per group of ``o.shape[1] // groups`` features: o / sqrt(mean(o^2) + eps) * weight *
-    sigmoid(gate).  ``o``: float32 [tokens, features]; ``weight``: float32, one entry per feature
+    f(gate), f the sigmoid or SiLU (``gate_function``).  ``o``: float32 [tokens, features]; ``weight``: float32, one entry per feature
     of a row or of a group; ``gate``: [tokens, features] in ``out_dtype``, rows may be strided."""
     _check(o, "o", torch.float32); _check(weight, "weight", torch.float32)
     ldg = _strided_rows(gate, "gate")
@@ -967,7 +1065,8 @@ def gated_norm(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: f
         raise KernelError("gated_norm: sizes do not match")
     out = torch.empty((tokens, features), dtype=out_dtype, device=o.device)
     _lib.core().call("mrun_gated_norm", _ptr(o), _ptr(weight), _c_int(weight.numel()), _ptr(gate), _c_long(ldg),
-                     dtype_code(out_dtype), _c_float(eps), _ptr(out), _c_int(tokens), _c_int(groups), _c_int(n), _stream())
+                     dtype_code(out_dtype), _c_float(eps), _ptr(out), _c_int(tokens), _c_int(groups), _c_int(n),
+                     _c_int(GATE_SHAPES[gate_function]), _stream())
     return out
 
 
@@ -1052,22 +1151,58 @@ def table_route(token_ids: torch.Tensor, table: torch.Tensor, experts: int, chos
     return weights
 
 
-def clamped_glu(u: torch.Tensor, weights: Optional[torch.Tensor], blocks: int, ff: int, limit: float, alpha: float) -> torch.Tensor:
+def clamped_glu(u: torch.Tensor, weights: Optional[torch.Tensor], blocks: int, ff: int, limit: float, alpha: float,
+                up_offset: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``u``: [rows, blocks * 2 * ff], a block of [gate | up] columns per expert.  Returns [rows,
-    blocks * ff]: min(gate, limit) * sigmoid(alpha * min(gate, limit)) * (clamp(up, +-limit) + 1),
-    times ``weights[row, block]`` (float32 [rows, blocks]) or ``weights[row]`` (float32 [rows])."""
-    _check(u, "u")
+    blocks * ff]: g * sigmoid(alpha * g) * (clamp(up, +-limit) + up_offset) with g = min(gate,
+    limit), times ``weights[row, block]`` (float32 [rows, blocks]) or ``weights[row]`` (float32
+    [rows]).  ``limit`` infinite: no clamp (alpha = 1 and up_offset = 0: SiLU(gate) * up).  ``u``,
+    ``weights`` and ``out`` may be column slices of wider matrices."""
+    ldu = _strided_rows(u, "u")
     rows = u.shape[0]
     if u.shape[1] != blocks * 2 * ff:
         raise KernelError(f"clamped_glu: u is {tuple(u.shape)}, expected width {blocks * 2 * ff}")
-    per_block = 0
+    per_block, ldw = 0, 0
     if weights is not None:
-        _check(weights, "weights", torch.float32)
-        if weights.shape == (rows, blocks) and weights.dim() == 2:
-            per_block = 1
-        elif weights.numel() != rows:
+        _check(weights, "weights", torch.float32, dense=False)
+        if weights.dim() == 2 and weights.shape == (rows, blocks) and weights.stride(1) == 1:
+            per_block, ldw = 1, weights.stride(0)
+        elif weights.dim() == 1 and weights.numel() == rows:
+            ldw = weights.stride(0)
+        elif weights.dim() == 2 and weights.shape == (rows, 1):
+            ldw = weights.stride(0)
+        else:
             raise KernelError(f"clamped_glu: weights {tuple(weights.shape)}")
-    act = torch.empty((rows, blocks * ff), dtype=u.dtype, device=u.device)
-    _lib.core().call("mrun_clamped_glu", _ptr(u), _ptr(act), dtype_code(u.dtype), _ptr(weights), _c_int(per_block),
-                     _c_int(rows), _c_int(blocks), _c_int(ff), _c_float(limit), _c_float(alpha), _stream())
-    return act
+    if out is None:
+        out = torch.empty((rows, blocks * ff), dtype=u.dtype, device=u.device)
+    lda = _strided_rows(out, "out")
+    if out.shape != (rows, blocks * ff) or out.dtype != u.dtype:
+        raise KernelError(f"clamped_glu: out is {tuple(out.shape)} {out.dtype}")
+    _lib.core().call("mrun_clamped_glu", _ptr(u), _c_long(ldu), _ptr(out), _c_long(lda), dtype_code(u.dtype), _ptr(weights),
+                     _c_long(ldw), _c_int(per_block), _c_int(rows), _c_int(blocks), _c_int(ff), _c_float(limit),
+                     _c_float(alpha), _c_float(up_offset), _stream())
+    return out
+
+
+def route_grouped(logits: torch.Tensor, experts: int, top: int, groups: int, keep: int, group_top: int, scale: float,
+                  chosen: Optional[torch.Tensor] = None):
+    """The choice of a router with sigmoid scores over groups of experts.  ``logits``: float32
+    [tokens, experts] or [tokens, experts + 1] (the last column the gate of a shared expert).
+    Returns (float32 [tokens, experts]: score / (sum of the chosen + 1e-20) * ``scale`` at the
+    chosen experts, zero elsewhere; float32 [tokens]: the sigmoid of the last column, or None).
+    The experts form ``groups`` equal groups of neighbours, a group's score is the sum of its
+    ``group_top`` largest scores, and only experts of the ``keep`` best groups can be chosen."""
+    _check(logits, "logits", torch.float32)
+    tokens, columns = logits.shape
+    if columns not in (experts, experts + 1):
+        raise KernelError(f"route_grouped: logits is {tuple(logits.shape)}, expected {experts} or {experts + 1} columns")
+    weights = torch.empty((tokens, experts), dtype=torch.float32, device=logits.device)
+    shared = torch.empty(tokens, dtype=torch.float32, device=logits.device) if columns > experts else None
+    if chosen is not None:
+        _check(chosen, "chosen", torch.int32)
+        if chosen.shape != (tokens, top):
+            raise KernelError(f"route_grouped: chosen is {tuple(chosen.shape)}, expected {(tokens, top)}")
+    _lib.core().call("mrun_route_grouped", _ptr(logits), _c_long(columns), _ptr(weights), _ptr(shared), _ptr(chosen),
+                     _c_int(tokens), _c_int(experts), _c_int(top), _c_int(groups), _c_int(keep), _c_int(group_top),
+                     _c_float(scale), _stream())
+    return weights, shared

@@ -1,10 +1,11 @@
 """Parts a layer is assembled from.  Importing the package registers the built-in kinds."""
-from . import (attention, block, channel_delta, decay_attention, differential_attention, feedforward, latent_attention,
-               norm, rotary, routed, table_routed, transforms)  # noqa: F401  (registration)
-from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, TRANSFORMS, Precision, Runtime,
-                   register_arrangement, register_feed_forward, register_mixer, register_norm,
+from . import (attention, block, channel_delta, decay_attention, differential_attention, embedding, feedforward,
+               gated_attention, gated_linear_attention, grouped_routed, latent_attention, norm, rotary, routed,
+               table_routed, transforms)  # noqa: F401  (registration)
+from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, TRANSFORMS, Precision, Runtime,
+                   register_arrangement, register_embedding, register_feed_forward, register_mixer, register_norm,
                    register_position, register_transform)
 
-__all__ = ["ARRANGEMENTS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "TRANSFORMS", "Precision", "Runtime",
-           "register_arrangement", "register_feed_forward", "register_mixer", "register_norm",
-           "register_position", "register_transform"]
+__all__ = ["ARRANGEMENTS", "EMBEDDINGS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "TRANSFORMS", "Precision",
+           "Runtime", "register_arrangement", "register_embedding", "register_feed_forward", "register_mixer",
+           "register_norm", "register_position", "register_transform"]

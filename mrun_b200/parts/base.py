@@ -26,6 +26,11 @@ feed-forward    ``forward(x, ctx) -> y``.
 arrangement     a block class built from a :class:`LayerSpec`; ``forward(resid, delta, ctx,
                 cache) -> delta`` takes the stream and the branch output not yet added to it and
                 returns the next pending branch output.
+embedding       in place of the plain table lookup (``ModelSpec.embedding``): ``forward(ctx, cache,
+                out, streams)`` fills the 32-bit stream tensor ``[tokens, streams * hidden]`` from
+                ``ctx.token_ids`` (every stream gets the same row); ``cache_need()`` may name
+                per-request state (``cache`` is then its :class:`EntryCache`), ``graph_safe`` as
+                for a mixer.  It binds the token table (``ModelSpec.embedding_name``) itself.
 transform       ``forward(x) -> x`` on the 32-bit stream right after the embedding
                 (``ModelSpec.embedding_transform``: a scale, an added table) or on the float32
                 logits of the wanted rows (``ModelSpec.logits_transform``: a soft cap, a bias);
@@ -110,6 +115,7 @@ MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 ARRANGEMENTS = Registry("arrangement")
 TRANSFORMS = Registry("transform")
+EMBEDDINGS = Registry("embedding")
 
 register_norm = NORMS.register
 register_position = POSITIONS.register
@@ -117,6 +123,7 @@ register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_arrangement = ARRANGEMENTS.register
 register_transform = TRANSFORMS.register
+register_embedding = EMBEDDINGS.register
 
 
 def local(tensors: Mapping[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor]:

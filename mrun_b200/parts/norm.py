@@ -29,6 +29,8 @@ class RMSNorm:
         weight = tensors["" if spec.bare else "weight"]
         if spec.scalar:             # one number for all coordinates: the kernels take it as a vector of equal entries
             weight = weight.reshape(1).expand(spec.size)
+        if spec.offset:             # stored around zero: the kernels take the scale itself
+            weight = weight.to(torch.float32) + float(spec.offset)
         self.weight = runtime.vector_f32(weight)
         self.act = runtime.precision.act
 

@@ -47,6 +47,8 @@ def scaled_frequencies(spec: ScaledRotarySpec):
     pairs = spec.dims // 2
     freq = torch.pow(torch.tensor(float(spec.base), dtype=torch.float64),
                      torch.arange(pairs, dtype=torch.float64) * (-2.0 / spec.dims))
+    if spec.linear_factor is not None:
+        freq = freq / float(spec.linear_factor)
     if spec.scaling is None:
         return freq, 1.0
     factor, original, fast, slow = (float(v) for v in spec.scaling)

@@ -66,9 +66,11 @@ def _register_builtin() -> None:
     from .config.qwen3 import Qwen3Config
     from .config.zasesun import ZasesunConfig
     from .config.balivik import BalivikConfig
+    from .config.fikudra import FikudraConfig
     register_architecture(Qwen3Config)
     register_architecture(ZasesunConfig)
     register_architecture(BalivikConfig)
+    register_architecture(FikudraConfig)
 
 
 _register_builtin()

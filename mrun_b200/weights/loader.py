@@ -38,8 +38,11 @@ class WeightsError(ValueError):
 
 def expected_tensors(spec: ModelSpec) -> List[TensorSpec]:
     """Every tensor the model binds, in a fixed order (embedding, head, layers, final norm)."""
-    from ..parts import ARRANGEMENTS, NORMS, TRANSFORMS
-    out = [TensorSpec(spec.embedding_name, (spec.vocab_size, spec.hidden_size))]
+    from ..parts import ARRANGEMENTS, EMBEDDINGS, NORMS, TRANSFORMS
+    if spec.embedding is not None:      # an embedding part binds the token table and what else it reads
+        out = list(EMBEDDINGS.tensor_specs(spec.embedding, spec.embedding_name))
+    else:
+        out = [TensorSpec(spec.embedding_name, (spec.vocab_size, spec.hidden_size))]
     if not spec.tie_embeddings:
         out.append(TensorSpec(spec.head_name, (spec.vocab_size, spec.hidden_size)))
     for layer in spec.layers:
