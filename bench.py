@@ -3,7 +3,7 @@
 random weights and seeded synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
-                    [--shape 8b|4b|32b] [--serve] [--design zasesun|balivik]
+                    [--shape 8b|4b|32b] [--serve] [--design zasesun|balivik|fikudra]
 
 A *step* is one decode step of a batch of 8 requests that each hold 1,024 tokens of context.
 ``value`` is decoded tokens per second over exactly K steps, timed on the device with CUDA events
@@ -18,6 +18,10 @@ routed feed-forwards) beside the Qwen3 decoder at equal widths, depths and head 
 2,048 tokens and decode at batch 8, each with its own FLOP and byte counts against the peaks.
 ``--design balivik`` does the same for the Balivik decoder (differential attention, decay attention
 and a channel-wise delta rule under four residual streams, dense and table-routed feed-forwards).
+``--design fikudra`` measures the Fikudra decoder (gated linear attention, attention with a sink and
+a gate per head that may read an earlier layer's pages, group-limited routed experts with a shared
+expert, four residual streams, a hashed bigram embedding) beside the Balivik decoder at equal
+widths, depths, head counts and expert sizes.
 """
 from __future__ import annotations
 
@@ -346,25 +350,92 @@ def balivik_counts(cfg: dict, tokens: int):
     return flops + 2.0 * cfg["vocab"] * h, row_bytes, state_bytes
 
 
+# Layer sizes for --design fikudra: (Fikudra sizes, the Balivik sizes of equal width, depth, head
+# counts and expert sizes, from the table above).  Eight layers: an attention, three gated linear
+# attentions, an attention that reads the first one's pages, three more linear attentions; keys and
+# values of one size (the tensor-core attention kernels), half of the features rotated; every layer
+# a mixture of 8 experts in 4 groups of which 2 stay, 2 chosen, with a shared expert; four streams.
+def _fikudra_sizes(width, heads, kv_heads, att_dim, dim, experts, top, expert_ff, shared_ff, rank, layers, vocab):
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": att_dim, "vdim": att_dim, "scale": att_dim ** -0.5,
+           "rot": {"base": 10000.0, "dims": att_dim // 2, "scaling": {"factor": 4.0}}}
+    gla = {"heads": heads, "dim": dim, "vdim": dim, "tau": 8.0, "rank": rank}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}
+
+    def entry(i):
+        if i % 4:
+            return {"type": "gla", "mixer": gla, "mlp": moe}
+        return {"type": "attention", "mixer": dict(att, kv_from=0) if i else att, "mlp": moe}
+    return {"architecture": "Fikudra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": 4,
+            "embedding": {"scale": 8.0, "bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 7}},
+            "layers": [entry(i) for i in range(layers)]}
+
+
+FIKUDRA_SIZES = {
+    "w2048": (_fikudra_sizes(2048, 16, 4, 128, 128, 8, 2, 2048, 2048, 128, 8, 32768), BALIVIK_SIZES["w2048"][0]),
+    "w4096": (_fikudra_sizes(4096, 32, 8, 128, 128, 8, 2, 3072, 3072, 256, 8, 32768), BALIVIK_SIZES["w4096"][0]),
+}
+
+
+def fikudra_counts(cfg: dict, tokens: int):
+    """(FLOPs of a prompt of ``tokens`` tokens as the design states them, bytes of one token's
+    cache rows over all layers, bytes of one request's recurrent states over all layers) of a
+    Fikudra configuration: products count two FLOPs a weight and token (a routed layer its chosen
+    experts and the shared one), an attention the scores and weighted sums of every visible key, a
+    linear attention the update and the read-out of its state for every token."""
+    h, flops, row_bytes, state_bytes = cfg["width"], 0.0, 0, 0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "attention":
+            own = m.get("kv_from") is None
+            params = h * (m["heads"] * (m["dim"] + m["vdim"] + 1) + (m["kv_heads"] * (m["dim"] + m["vdim"]) if own else 0))
+            flops += 2.0 * (tokens * tokens / 2.0) * m["heads"] * (m["dim"] + m["vdim"])
+            row_bytes += 2 * m["kv_heads"] * (m["dim"] + m["vdim"])       # read by every layer that uses these pages
+        else:
+            keyed, inner = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            params = h * (2 * keyed + 3 * inner + m["rank"]) + keyed * m["rank"]
+            flops += 2.0 * tokens * m["heads"] * 2 * m["dim"] * m["vdim"]
+            state_bytes += 4 * m["heads"] * m["dim"] * m["vdim"]
+        mlp = layer["mlp"]
+        if mlp and mlp["kind"] == "dense":
+            params += 3 * h * mlp["ff"]
+        elif mlp:
+            shared = (mlp.get("shared") or {}).get("ff", 0)
+            params += h * (mlp["router"]["experts"] + 1) + 3 * h * (mlp["router"]["top"] * mlp["expert"]["ff"] + shared)
+        flops += 2.0 * tokens * params
+    return flops + 2.0 * cfg["vocab"] * h, row_bytes, state_bytes
+
+
 def compare_designs(args, peaks: dict) -> int:
     """Prefill of 2,048 tokens and decode at batch 8 with 1,024-token contexts, the named design
-    beside Qwen3 at equal sizes, each through the same ``Executor.step`` and captured decode step."""
+    beside Qwen3 (Fikudra: beside Balivik) at equal sizes, each through the same ``Executor.step``
+    and captured decode step."""
     import torch
     from mrun_b200 import Engine
     from mrun_b200.config import Qwen3Config, ZasesunConfig
     from mrun_b200.config.balivik import BalivikConfig
+    from mrun_b200.config.fikudra import FikudraConfig
     from mrun_b200.engine import StepEntry
     context, batch = 1024, 8
     out = {}
     sampler = ClockSampler()
     sampler.start()
-    size_sets = DESIGN_SIZES if args.design == "zasesun" else BALIVIK_SIZES
+    size_sets = {"zasesun": DESIGN_SIZES, "balivik": BALIVIK_SIZES, "fikudra": FIKUDRA_SIZES}[args.design]
+    beside = "balivik" if args.design == "fikudra" else "qwen3"
     for name in (args.sizes.split(",") if args.sizes else sorted(size_sets)):
         z_sizes, q_sizes = size_sets[name]
         row = {}
-        for design in (args.design, "qwen3"):
+        for design in (args.design, beside):
             state_bytes = 0
-            if design == "zasesun":
+            if design == "fikudra":
+                config = FikudraConfig.from_dict(z_sizes)
+                vocab, h = z_sizes["vocab"], z_sizes["width"]
+                flops, kv_bytes, state_bytes = fikudra_counts(z_sizes, PREFILL_TOKENS)
+            elif design == "balivik" and args.design == "fikudra":
+                config = BalivikConfig.from_dict(q_sizes)
+                vocab, h = q_sizes["vocab"], q_sizes["width"]
+                flops, kv_bytes, state_bytes = balivik_counts(q_sizes, PREFILL_TOKENS)
+            elif design == "zasesun":
                 config = ZasesunConfig.from_dict(z_sizes)
                 vocab, h = z_sizes["vocab"], z_sizes["width"]
                 flops, kv_bytes = zasesun_counts(z_sizes, PREFILL_TOKENS)
@@ -417,7 +488,7 @@ def compare_designs(args, peaks: dict) -> int:
             del engine, executor, requests
             torch.cuda.empty_cache()
         out[name] = row
-    print(json.dumps({"metric": f"prefill and decode tok/s, {args.design.capitalize()} beside Qwen3 at equal sizes (bf16)", "unit": "tok/s",
+    print(json.dumps({"metric": f"prefill and decode tok/s, {args.design.capitalize()} beside {beside.capitalize()} at equal sizes (bf16)", "unit": "tok/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "dtype": "bf16",
                       "data": "synthetic (seeded uniform token ids, N(0,0.02) weights)",
                       "config": {"prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "context": context,
@@ -455,8 +526,8 @@ def main() -> int:
     parser.add_argument("--profiler-range", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                         help="bracket the timed decode steps (or the last timed prefill) with "
                              "cudaProfilerStart/Stop, for a profiler started with --profile-from-start off")
-    parser.add_argument("--design", choices=["zasesun", "balivik"], default=None,
-                        help="instead of the default workload: the named design beside Qwen3 at equal sizes "
+    parser.add_argument("--design", choices=["zasesun", "balivik", "fikudra"], default=None,
+                        help="instead of the default workload: the named design beside Qwen3 (fikudra: beside Balivik) at equal sizes "
                              "(prefill of 2,048 tokens, decode at batch 8)")
     parser.add_argument("--sizes", default=None, help="with --design: which of its size sets to run, comma separated")
     args = parser.parse_args()

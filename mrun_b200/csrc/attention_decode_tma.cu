@@ -180,7 +180,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                   const int* __restrict__ positions, const int* __restrict__ tile_prefix,
                   const int4* __restrict__ assignment, int tokens, float* __restrict__ part_o,
                   float* __restrict__ part_ml, int* __restrict__ counters, int heads, int kv_heads, int page_size,
-                  int page_shift, float scale_log2, int window, const FusedInput fused, int* __restrict__ status) {
+                  int page_shift, float scale_log2, int window, float sink_log2, const FusedInput fused, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int group = heads / kv_heads;
@@ -409,6 +409,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     ll += src[D + 1] * c;
                 }
                 if (sg.complete) {
+                    ll = with_sink(ll, mm, sink_log2);
                     const float inv = ll > 0.f ? 1.f / ll : 0.f;
                     __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
                     __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
@@ -478,6 +479,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                                 ll += ml[k].y * c;
                             }
                         }
+                        ll = with_sink(ll, mm, sink_log2);
                         const float inv = ll > 0.f ? 1.f / ll : 0.f;
                         __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
                         __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
@@ -537,7 +539,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                       const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
                       const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
                       const int* __restrict__ positions, int heads, int kv_heads, int page_size, int page_shift,
-                      float scale_log2, int window, const FusedInput fused, int* __restrict__ status) {
+                      float scale_log2, int window, float sink_log2, const FusedInput fused, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int group = heads / kv_heads;
@@ -768,6 +770,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                 ll += src[D + 1] * c;
             }
             if (pieces == 1) {
+                ll = with_sink(ll, mm, sink_log2);
                 const float inv = ll > 0.f ? 1.f / ll : 0.f;
                 __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
                 __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
@@ -816,6 +819,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                         ll += ml[k].y * c;
                     }
                 }
+                ll = with_sink(ll, mm, sink_log2);
                 const float inv = ll > 0.f ? 1.f / ll : 0.f;
                 __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
                 __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
@@ -877,7 +881,7 @@ namespace {
 template <int RING>
 int launch_cluster(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* q, long q_stride, void* out,
                    const int* block_tables, int max_blocks, const int* token_slot, const int* positions, int tokens,
-                   int cluster, int heads, int kv_heads, int page_size, float scale, int window, const FusedInput& in,
+                   int cluster, int heads, int kv_heads, int page_size, float scale, int window, float sink, const FusedInput& in,
                    int* status, cudaStream_t stream) {
     const int group = heads / kv_heads;
     const size_t smem = tma_smem_bytes(RING, group);
@@ -903,7 +907,7 @@ int launch_cluster(const CUtensorMap& map_k, const CUtensorMap& map_v, const voi
     config.numAttrs = 1;
     MRUN_CHECK_CUDA(cudaLaunchKernelEx(&config, decode_cluster_kernel<RING>, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out,
                                        block_tables, max_blocks, token_slot, positions, heads, kv_heads, page_size,
-                                       page_shift_of(page_size), scale * LOG2E, window, in, status),
+                                       page_shift_of(page_size), scale * LOG2E, window, sink * LOG2E, in, status),
                     "attn_decode_cluster");
     return 0;
 }
@@ -929,7 +933,7 @@ MRUN_API int mrun_attn_decode_cluster_max(int group) {
 MRUN_API int mrun_attn_decode_cluster(const void* q, long q_stride, void* out, void* k_cache, void* v_cache,
                                       const int* block_tables, int max_blocks, const int* token_slot,
                                       const int* positions, int tokens, int cluster, int heads, int kv_heads,
-                                      int head_dim, int page_size, float scale, int window, int fused,
+                                      int head_dim, int page_size, float scale, int window, float sink, int fused,
                                       const float* q_weight, const float* k_weight, float eps, const float* rot,
                                       int rotary_dim, const int* slots, const int* rows, long pages, int* status,
                                       cudaStream_t stream) {
@@ -971,9 +975,9 @@ MRUN_API int mrun_attn_decode_cluster(const void* q, long q_stride, void* out, v
     in.rows = rows;
     if (ring_for(group) == 3)
         return launch_cluster<3>(map_k, map_v, q, q_stride, out, block_tables, max_blocks, token_slot, positions, tokens,
-                                 cluster, heads, kv_heads, page_size, scale, window, in, status, stream);
+                                 cluster, heads, kv_heads, page_size, scale, window, sink, in, status, stream);
     return launch_cluster<2>(map_k, map_v, q, q_stride, out, block_tables, max_blocks, token_slot, positions, tokens, cluster,
-                             heads, kv_heads, page_size, scale, window, in, status, stream);
+                             heads, kv_heads, page_size, scale, window, sink, in, status, stream);
 #else
     return mrun_set_error("attn_decode_cluster: not built for head_dim=%d (head sizes 64 and 128 only)", MRUN_HEAD_DIM);
 #endif
@@ -988,7 +992,7 @@ MRUN_API int mrun_attn_decode_tma(const void* q, long q_stride, void* out, void*
                                   const int* block_tables, int max_blocks, const int* token_slot,
                                   const int* positions, const int* tile_prefix, const int* assignment, int tokens,
                                   float* part_o, float* part_ml, int* counters, int blocks, int heads, int kv_heads,
-                                  int head_dim, int page_size, float scale, int window, int fused,
+                                  int head_dim, int page_size, float scale, int window, float sink, int fused,
                                   const float* q_weight, const float* k_weight, float eps, const float* rot,
                                   int rotary_dim, const int* slots, const int* rows, long pages, int* status,
                                   cudaStream_t stream) {
@@ -1034,12 +1038,12 @@ MRUN_API int mrun_attn_decode_tma(const void* q, long q_stride, void* out, void*
         decode_tma_kernel<3><<<dim3(blocks), TMA_THREADS, smem, stream>>>(
             map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, block_tables, max_blocks, token_slot, positions,
             tile_prefix, (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads, page_size,
-            page_shift_of(page_size), scale * LOG2E, window, in, status);
+            page_shift_of(page_size), scale * LOG2E, window, sink * LOG2E, in, status);
     else
         decode_tma_kernel<2><<<dim3(blocks), TMA_THREADS, smem, stream>>>(
             map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, block_tables, max_blocks, token_slot, positions,
             tile_prefix, (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads, page_size,
-            page_shift_of(page_size), scale * LOG2E, window, in, status);
+            page_shift_of(page_size), scale * LOG2E, window, sink * LOG2E, in, status);
     MRUN_CHECK_LAUNCH("attn_decode_tma");
     return 0;
 #else

@@ -156,7 +156,7 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
                const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
                const int* __restrict__ positions, const int* __restrict__ tile_tok0,
                const int* __restrict__ tile_ntok, int heads, int kv_heads, int page_size, int page_shift,
-               float scale_log2, int window) {
+               float scale_log2, int window, float sink_log2) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [64][LD]
     bf16* k_tiles = q_tile + 64 * LD;                           // [2][64][LD]
@@ -237,6 +237,8 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     }
+    l[0] = with_sink(l[0], m[0], sink_log2);
+    l[1] = with_sink(l[1], m[1], sink_log2);
     const float inv0 = l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
     bf16* stage_rows = q_tile + w_row0 * LD;
 #pragma unroll
@@ -421,7 +423,7 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
               const int* __restrict__ positions, const int* __restrict__ tile_prefix,
               const int4* __restrict__ assignment, int tokens, float* __restrict__ part_o,
               float* __restrict__ part_ml, int* __restrict__ counters, int heads, int kv_heads, int page_size,
-              int page_shift, float scale_log2, int window, const FusedInput fused) {
+              int page_shift, float scale_log2, int window, float sink_log2, const FusedInput fused) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [16][LD]
     bf16* k_tiles = q_tile + 16 * LD;                           // [STAGES][64][LD]
@@ -609,6 +611,7 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
                 ll += src[D + 1] * c;
             }
             if (complete) {
+                ll = with_sink(ll, mm, sink_log2);
                 out[((size_t)tok * heads + kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
             } else {
                 part_o[(my_slot * 16 + row) * D + d] = acc;
@@ -674,6 +677,7 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
                             ll += ml[k].y * c;
                         }
                     }
+                    ll = with_sink(ll, mm, sink_log2);
                     const float inv = ll > 0.f ? 1.f / ll : 0.f;
                     __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
                     __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
@@ -705,7 +709,7 @@ MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const vo
                                const int* block_tables, int max_blocks, const int* token_slot,
                                const int* positions, const int* tile_tok0, const int* tile_ntok, int n_tiles,
                                int heads, int kv_heads, int head_dim, int page_size, float scale, int window,
-                               cudaStream_t stream) {
+                               float sink, cudaStream_t stream) {
     if (int rc = check_common("attn_prefill", heads, kv_heads, head_dim, page_size, max_blocks, window, 64)) return rc;
     MRUN_REQUIRE(n_tiles >= 0, "attn_prefill: n_tiles=%d", n_tiles);
     if (n_tiles == 0) return 0;
@@ -720,7 +724,7 @@ MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const vo
         prefill_kernel<<<dim3(kv_heads, now), THREADS, PREFILL_SMEM, stream>>>(
             (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
             token_slot, positions, tile_tok0 + done, tile_ntok + done, heads, kv_heads, page_size, page_shift_of(page_size),
-            scale * LOG2E, window);
+            scale * LOG2E, window, sink * LOG2E);
         MRUN_CHECK_LAUNCH("attn_prefill");
     }
     return 0;
@@ -769,7 +773,7 @@ MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, void* k_c
                               const int* block_tables, int max_blocks, const int* token_slot,
                               const int* positions, const int* tile_prefix, const int* assignment, int tokens,
                               float* part_o, float* part_ml, int* counters, int blocks, int heads, int kv_heads,
-                              int head_dim, int page_size, float scale, int window, int fused,
+                              int head_dim, int page_size, float scale, int window, float sink, int fused,
                               const float* q_weight, const float* k_weight, float eps, const float* rot,
                               int rotary_dim, const int* slots, cudaStream_t stream) {
     if (int rc = check_common("attn_decode", heads, kv_heads, head_dim, page_size, max_blocks, window, 16)) return rc;
@@ -805,7 +809,7 @@ MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, void* k_c
                                      (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                      block_tables, max_blocks, token_slot, positions, tile_prefix,
                                      (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads,
-                                     page_size, page_shift_of(page_size), scale * LOG2E, window, in),
+                                     page_size, page_shift_of(page_size), scale * LOG2E, window, sink * LOG2E, in),
                     "attn_decode");
     return 0;
 }
@@ -901,7 +905,7 @@ MRUN_API int mrun_attn_decode_static(const void* q, long q_stride, void* out, co
     decode_kernel<<<dim3(blocks), THREADS, DECODE_SMEM, stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
         token_slot, positions, tile_prefix, (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads,
-        page_size, page_shift_of(page_size), scale * LOG2E, window, FusedInput{});
+        page_size, page_shift_of(page_size), scale * LOG2E, window, -INFINITY, FusedInput{});
     MRUN_CHECK_LAUNCH("attn_decode_static");
     return 0;
 }

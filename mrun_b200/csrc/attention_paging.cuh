@@ -31,3 +31,9 @@ inline int page_shift_of(int page_size) {
         if ((1 << s) == page_size) return s;
     return -1;
 }
+
+// A softmax sink: one more term of score `sink_log2` (in the kernels' base-2 units; -infinity:
+// none) that has no value, added to the denominator `l` of a row whose running maximum is `m`.
+__device__ __forceinline__ float with_sink(float l, float m, float sink_log2) {
+    return sink_log2 > -INFINITY ? l + exp2f(sink_log2 - m) : l;
+}

@@ -116,7 +116,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                    const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
                    const int* __restrict__ positions, const int* __restrict__ tile_tok0,
                    const int* __restrict__ tile_ntok, int heads, int kv_heads, int page_size, int page_shift,
-                   float scale_log2, int window, int* __restrict__ status) {
+                   float scale_log2, int window, float sink_log2, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_tile = base;
@@ -310,7 +310,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         pair_sync(quarter);
         if (alive) {
             tc_fence_after();
-            const float total = l + pair_sum[half ^ 1][row];
+            const float total = with_sink(l + pair_sum[half ^ 1][row], m_used, sink_log2);
             const float inv = total > 0.f ? 1.f / total : 0.f;
             bf16* dst = out + ((size_t)(tok0 + row / group) * heads + kvh * group + row % group) * D + half * O_HALF;
 #pragma unroll 1
@@ -456,7 +456,7 @@ MRUN_API int mrun_attn_prefill_tc5(const void* q, long q_stride, void* out, cons
                                    const void* v_cache, const int* block_tables, int max_blocks,
                                    const int* token_slot, const int* positions, const int* tile_tok0,
                                    const int* tile_ntok, int n_tiles, int heads, int kv_heads, int head_dim,
-                                   int page_size, float scale, int window, long pages, int* status,
+                                   int page_size, float scale, int window, float sink, long pages, int* status,
                                    cudaStream_t stream) {
 #if MRUN_ATTN_TC5
     MRUN_REQUIRE(head_dim == D, "attn_prefill_tc5: this library was built for head_dim=%d, got %d", D, head_dim);
@@ -488,7 +488,7 @@ MRUN_API int mrun_attn_prefill_tc5(const void* q, long q_stride, void* out, cons
         prefill_tc5_kernel<<<dim3(kv_heads, now), THREADS, SMEM_BYTES, stream>>>(
             map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, block_tables, max_blocks,
             token_slot, positions, tile_tok0 + done, tile_ntok + done, heads, kv_heads, page_size, page_shift_of(page_size),
-            scale * LOG2E, window, status);
+            scale * LOG2E, window, sink * LOG2E, status);
         MRUN_CHECK_LAUNCH("attn_prefill_tc5");
     }
     return 0;

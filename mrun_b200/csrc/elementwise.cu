@@ -691,3 +691,36 @@ MRUN_API int mrun_select_tokens(int* ids, const int* previous, const int* source
     return 0;
 }
 
+
+// ------------------------------------------------------------------------------------------
+// A gate per head, in place: y[t, h, :] *= sigmoid(gate[t, h]).  `gate` rows are `ldg` elements
+// apart (a column slice of a wider product); the sigmoid is 32-bit.  For attention kernels that
+// write finished heads and know nothing of a gate.
+// ------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void head_gate_kernel(TA* __restrict__ y, const TA* __restrict__ gate, long ldg, long total, int heads, int n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long pair = i / n;                 // (token, head)
+    const long t = pair / heads;
+    const float g = to_float(gate[t * ldg + (pair - t * heads)]);
+    y[i] = from_float<TA>(to_float(y[i]) / (1.f + expf(-g)));
+}
+
+MRUN_API int mrun_head_gate(void* y, const void* gate, long ldg, int act_dtype, int tokens, int heads, int n,
+                            cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && heads > 0 && n > 0 && ldg >= heads, "head_gate: bad sizes tokens=%d heads=%d n=%d ldg=%ld",
+                 tokens, heads, n, ldg);
+    if (tokens == 0) return 0;
+    const long total = (long)tokens * heads * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (act_dtype == MRUN_F32)
+        head_gate_kernel<float><<<blocks, 256, 0, stream>>>((float*)y, (const float*)gate, ldg, total, heads, n);
+    else if (act_dtype == MRUN_BF16)
+        head_gate_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)gate, ldg, total,
+                                                                    heads, n);
+    else
+        return mrun_set_error("head_gate: unknown dtype code %d", act_dtype);
+    MRUN_CHECK_LAUNCH("head_gate");
+    return 0;
+}

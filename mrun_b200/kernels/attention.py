@@ -21,6 +21,7 @@ the fused norm/rotary/cache kernel just before.
 from __future__ import annotations
 
 import ctypes
+import math
 
 import numpy as np
 import torch
@@ -220,17 +221,20 @@ def latent_wide_ok(dtype: torch.dtype, width: int, value_dim: int) -> bool:
 
 
 def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, group, ctx,
-                    heads: int, scale: float, window: int, raw=None, value_dim: int = 0) -> torch.Tensor:
+                    heads: int, scale: float, window: int, raw=None, value_dim: int = 0,
+                    sink: bool = False) -> torch.Tensor:
     """``q``: the step's queries (row t at ``q_stride * t``, heads contiguous); ``cache``: the
     schedule entry's pages; ``group``: the step's view of the cache's group.  ``raw``, only where
     :func:`decode_fuses_input` holds: ``(q_weight, k_weight, eps, rot, rotary_dim, slots)`` for a
     ``q`` that is the projection's raw [q | k | v] rows.  ``value_dim``, for a cache whose rows
     are key and value at once (one tensor of pages, one kv head): how many of a row's first
     features the caller reads of the output; rows too wide for the per-head-size kernels then go
-    to the kernel for wide latent rows."""
+    to the kernel for wide latent rows.  ``sink``: one more term of score 0 without a value in
+    every softmax's denominator (it enters where a kernel normalises a finished row, after the
+    pieces of split keys have been merged)."""
     pages, kv_heads, page_size, head_dim = cache.k.shape
     ratio = heads // kv_heads
-    if (value_dim and cache.v is cache.k and kv_heads == 1 and window == 0 and raw is None
+    if (value_dim and cache.v is cache.k and kv_heads == 1 and window == 0 and raw is None and not sink
             and not supports_tensor_cores(q.dtype, head_dim, ratio) and latent_wide_ok(q.dtype, head_dim, value_dim)):
         ops._check(q, "q", torch.bfloat16, dense=False); ops._check(out, "out", torch.bfloat16)
         # few tokens and long contexts: every token's keys are dealt to several blocks, so that the
@@ -251,13 +255,13 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
         return out
     if not supports_tensor_cores(q.dtype, head_dim, ratio):
         return ops.paged_attention_generic(q, q_stride, out, cache.k, cache.v, group.block_tables,
-                                           ctx.token_slot, ctx.positions, heads, scale, window)
+                                           ctx.token_slot, ctx.positions, heads, scale, window, sink=sink)
     library = _lib.attention(head_dim)
     tokens = ctx.num_tokens
     common = (_ptr(cache.k), _ptr(cache.v), _ptr(group.block_tables), _c_int(group.max_blocks),
               _ptr(ctx.token_slot), _ptr(ctx.positions))
     tail = (_c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale),
-            _c_int(window), _stream())
+            _c_int(window), _c_float(0.0 if sink else -math.inf), _stream())
     if ctx.all_decode and ratio <= 16:
         if tokens * kv_heads > COUNTER_CAPACITY:
             raise ValueError(f"a decode step of {tokens} tokens x {kv_heads} kv heads exceeds {COUNTER_CAPACITY} pairs")

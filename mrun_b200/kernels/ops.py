@@ -1070,6 +1070,19 @@ def gated_norm(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: f
     return out
 
 
+def head_gate(y: torch.Tensor, gate: torch.Tensor, heads: int) -> torch.Tensor:
+    """In place: every head of ``y`` ([tokens, heads * n]) times the 32-bit sigmoid of its entry
+    of ``gate`` ([tokens, heads] in the dtype of ``y``, rows may be strided)."""
+    _check(y, "y")
+    ldg = _strided_rows(gate, "gate")
+    tokens, features = y.shape
+    if gate.shape != (tokens, heads) or gate.dtype != y.dtype or features % heads:
+        raise KernelError("head_gate: sizes do not match")
+    _lib.core().call("mrun_head_gate", _ptr(y), _ptr(gate), _c_long(ldg), dtype_code(y.dtype), _c_int(tokens), _c_int(heads),
+                     _c_int(features // heads), _stream())
+    return y
+
+
 # ------------------------------------------------------------------ differential attention
 
 def diff_rope_cache(qkv: torch.Tensor, rot: Optional[torch.Tensor], rot_dims: int, slots: Optional[torch.Tensor],

@@ -14,6 +14,8 @@ on CUDA cores in 32-bit arithmetic with sink and gate inside the kernel.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..cache.needs import PagedKV
@@ -23,7 +25,9 @@ from ..kernels.attention import paged_attention, supports_tensor_cores
 from .base import POSITIONS, Runtime, register_mixer
 
 
-TENSOR_CORES = False     # False: the CUDA-core kernel for every shape (tests compare the two)
+# False (``MRUN_GATED_ATTENTION_TENSOR_CORES=0`` in the environment): the CUDA-core kernel for every
+# shape (tests compare the two)
+TENSOR_CORES = os.environ.get("MRUN_GATED_ATTENTION_TENSOR_CORES", "1") != "0"
 
 
 @register_mixer("gated_attention")
@@ -58,6 +62,9 @@ class GatedAttention:
         self.gate_off = sum(p.shape[0] for p in parts)
         if spec.head_gate:
             parts.append(tensors["g"])
+        rows = sum(p.shape[0] for p in parts)
+        if rows % 8:        # rows of the product's output start on 16 bytes, as the tensor-core kernels read q
+            parts.append(torch.zeros((8 - rows % 8, spec.hidden), dtype=parts[0].dtype, device=parts[0].device))
         self.w_in = runtime.matrix(torch.cat(parts, dim=0))
         self.w_o = runtime.matrix(tensors["o"])
         self.q_weight = self.k_weight = None

@@ -16,7 +16,9 @@ from .base import Runtime, register_norm
 class RMSNorm:
     @staticmethod
     def tensor_specs(spec: RMSNormSpec, prefix: str):
-        return [TensorSpec(prefix if spec.bare else f"{prefix}.weight", () if spec.scalar else (spec.size,), "norm")]
+        # a scale stored minus an offset lies around zero, not around one
+        return [TensorSpec(prefix if spec.bare else f"{prefix}.weight", () if spec.scalar else (spec.size,),
+                           "norm_zero" if spec.offset else "norm")]
 
     # ``delta`` may be a product that has not run yet (``ops.PendingLinear``): with a handful
     # of rows it runs with the residual sum and this norm folded into its epilogue, and what

@@ -36,6 +36,10 @@ def random_tensor(t: TensorSpec, seed: int, std: float, norm_noise: float, dtype
             return torch.ones(t.shape, dtype=dtype, device=device)
         noise = torch.randn(t.shape, generator=gen, dtype=torch.float32, device=device)
         return (1.0 + norm_noise * noise).to(dtype)
+    if t.init == "norm_zero":           # scale vectors stored around zero: 0, or N(0, norm_noise)
+        if norm_noise == 0.0:
+            return torch.zeros(t.shape, dtype=dtype, device=device)
+        return (norm_noise * torch.randn(t.shape, generator=gen, dtype=torch.float32, device=device)).to(dtype)
     if t.init.startswith("table:"):
         # every row names different entries of range(n), as many as the row is long
         n = int(t.init.split(":")[1])

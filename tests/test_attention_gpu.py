@@ -187,7 +187,7 @@ def test_decode_tiles_dealt_to_any_number_of_blocks(blocks, min_tiles, splits, e
             _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
             _ptr(plan), _ptr(assignment), _c_int(n), _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(blocks),
             _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale), _c_int(0),
-            _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None), *extra, _stream())
+            _c_float(float("-inf")), _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None), *extra, _stream())
         got = out.float().cpu()
         assert int(status.item()) == 0
         assert (got - want).abs().max() <= 2e-2 * want.abs().max()
@@ -264,7 +264,7 @@ def test_decode_contexts_of_unequal_length_and_raw_input(contexts, blocks, min_t
             _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
             _ptr(plan), _ptr(assignment), _c_int(n), _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(blocks),
             _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale), _c_int(0),
-            *fused, *extra, _stream())
+            _c_float(float("-inf")), *fused, *extra, _stream())
         got = out.float().cpu()
         assert int(status.item()) == 0
         assert (got - want).abs().max() <= 2e-2 * want.abs().max()
@@ -325,7 +325,7 @@ def test_cluster_decode_with_every_cluster_size(cluster, heads, kv_heads, head_d
             "mrun_attn_decode_cluster", _ptr(q_in), _c_long(q_in.stride(0)), _ptr(out), _ptr(k_got), _ptr(v_got),
             _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
             _c_int(n), _c_int(cluster), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size),
-            _c_float(scale), _c_int(window), *fused, _ptr(None), _c_long(case.kd.shape[0]), _ptr(status), _stream())
+            _c_float(scale), _c_int(window), _c_float(float("-inf")), *fused, _ptr(None), _c_long(case.kd.shape[0]), _ptr(status), _stream())
         got = out.float().cpu()
         assert int(status.item()) == 0
         assert (got - want).abs().max() <= 2e-2 * want.abs().max()
@@ -348,7 +348,7 @@ def test_cluster_decode_refuses_what_it_cannot_take():
             "mrun_attn_decode_cluster", _ptr(case.qd), _c_long(case.qd.stride(0)), _ptr(out), _ptr(case.kd), _ptr(case.vd),
             _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
             _c_int(1), _c_int(cluster), _c_int(heads), _c_int(2), _c_int(64), _c_int(16), _c_float(0.125), _c_int(0),
-            _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None), _ptr(None),
+            _c_float(float("-inf")), _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None), _ptr(None),
             _c_long(case.kd.shape[0]), _ptr(status), _stream())
     with pytest.raises(KernelError, match="query heads per kv head exceed"):
         call(4, 32)

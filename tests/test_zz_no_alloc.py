@@ -38,7 +38,7 @@ def call_decode(dll, name, case, out, blocks, min_tiles, scratch=None):
         return fn(*head, _c_int(n), _c_int(blocks), _c_int(min_tiles), *shape, _stream())
     plan, assignment, part_o, part_ml, counters = scratch
     # the ordinary entry point also takes the description of raw q, k, v rows; here q is ready
-    ready = (_c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None))
+    ready = (_c_float(float("-inf")), _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None))   # no sink
     return fn(*head, _ptr(plan), _ptr(assignment), _c_int(n), _ptr(part_o), _ptr(part_ml), _ptr(counters),
               _c_int(blocks), *shape, *ready, _stream())
 
