@@ -69,8 +69,10 @@ def attention_keys_values(m, W, p, h, eps, positions):
 
 def sink_softmax(s, mask):
     """exp(s_j) / (1 + sum over the visible j of exp(s_j)) along the last axis."""
-    e = torch.where(mask, torch.exp(s), torch.zeros_like(s))
-    return e / (1.0 + e.sum(-1, keepdim=True))
+    s = torch.where(mask, s, torch.full_like(s, float("-inf")))
+    top = s.max(-1, keepdim=True).values.clamp_min(0.0)         # the sink's score 0 takes part in the maximum
+    e = torch.exp(s - top)
+    return e / (torch.exp(-top) + e.sum(-1, keepdim=True))
 
 
 def attention(m, W, p, h, eps, positions, keys_values):

@@ -92,6 +92,19 @@ FTINY = {
                 "layers": [layer("gla", gla(5, 16, 16, 32.0, 10), moe(8, 4, 16, groups=4, keep=2, scale=2.5, shared=8)),
                            layer("attention", attention(8, 1, 32, 16, 0.18, rot_dims=16, base=10000.0, factor=1.5), None)]},
         seed=13, std=0.1, norm_noise=0.2, page_size=16),
+    # every expert of every routed layer is chosen (as many groups kept as there are), so that no
+    # choice is a close call and a bfloat16 run is compared at every position; keys and values of
+    # 64 with half of the features rotated; three streams; a dense feed-forward under the reading layer
+    "T": dict(
+        config={"architecture": "Fikudra", "vocab": 200, "width": 72, "norm": {"eps": 1e-5}, "streams": 3,
+                "embedding": {"scale": 2.0, "bigram": {"buckets": 37, "mul_prev": 11, "mul_cur": 29}},
+                "layers": [layer("attention", attention(4, 2, 64, 64, 0.15, rot_dims=32, base=5000.0, factor=2.5),
+                                 moe(4, 4, 16, shared=16)),
+                           layer("gla", gla(3, 32, 24, 8.0, 6), moe(6, 6, 8, groups=3, keep=3, scale=1.5)),
+                           layer("attention", attention(4, 2, 64, 64, 0.15, rot_dims=32, base=5000.0, factor=2.5, kv_from=0),
+                                 {"kind": "dense", "ff": 48}),
+                           layer("gla", gla(2, 16, 48, 2.0, 4), None)]},
+        seed=21, std=0.1, norm_noise=0.2, page_size=16),
 }
 
 
