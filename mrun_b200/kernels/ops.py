@@ -1204,18 +1204,22 @@ def route_grouped(logits: torch.Tensor, experts: int, top: int, groups: int, kee
     Returns (float32 [tokens, experts]: score / (sum of the chosen + 1e-20) * ``scale`` at the
     chosen experts, zero elsewhere; float32 [tokens]: the sigmoid of the last column, or None).
     The experts form ``groups`` equal groups of neighbours, a group's score is the sum of its
-    ``group_top`` largest scores, and only experts of the ``keep`` best groups can be chosen."""
-    _check(logits, "logits", torch.float32)
+    ``group_top`` largest scores, and only experts of the ``keep`` best groups can be chosen.
+    ``logits`` may be the first columns of wider rows (a product padded to a vendor-friendly
+    width): its row stride is passed on."""
+    _check(logits, "logits", torch.float32, dense=False)
     tokens, columns = logits.shape
     if columns not in (experts, experts + 1):
         raise KernelError(f"route_grouped: logits is {tuple(logits.shape)}, expected {experts} or {experts + 1} columns")
+    if logits.stride(1) != 1 or logits.stride(0) < columns:
+        raise KernelError(f"route_grouped: logits has strides {logits.stride()}, expected rows of unit stride")
     weights = torch.empty((tokens, experts), dtype=torch.float32, device=logits.device)
     shared = torch.empty(tokens, dtype=torch.float32, device=logits.device) if columns > experts else None
     if chosen is not None:
         _check(chosen, "chosen", torch.int32)
         if chosen.shape != (tokens, top):
             raise KernelError(f"route_grouped: chosen is {tuple(chosen.shape)}, expected {(tokens, top)}")
-    _lib.core().call("mrun_route_grouped", _ptr(logits), _c_long(columns), _ptr(weights), _ptr(shared), _ptr(chosen),
+    _lib.core().call("mrun_route_grouped", _ptr(logits), _c_long(logits.stride(0)), _ptr(weights), _ptr(shared), _ptr(chosen),
                      _c_int(tokens), _c_int(experts), _c_int(top), _c_int(groups), _c_int(keep), _c_int(group_top),
                      _c_float(scale), _stream())
     return weights, shared

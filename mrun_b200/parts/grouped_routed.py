@@ -54,7 +54,13 @@ class GroupedRoutedMLP:
         self.alpha = ACTIVATIONS[spec.activation]
         names = [f"e{e}" for e in range(spec.experts)] + (["shared"] if spec.shared_ff else [])
         self.gated_shared = bool(spec.shared_ff and spec.shared_gate)
-        self.w_router = runtime.matrix(torch.cat([tensors["router"]] + ([tensors["shared.sg"]] if self.gated_shared else []), dim=0))
+        router = torch.cat([tensors["router"]] + ([tensors["shared.sg"]] if self.gated_shared else []), dim=0)
+        self.router_rows = router.shape[0]
+        if runtime.precision.act == torch.bfloat16 and router.shape[0] % 8:
+            # zero rows up to a multiple of 8: the vendor library's tensor-core kernels of this
+            # architecture want rows of 16 bytes; the route kernel reads the first columns only
+            router = torch.cat([router, router.new_zeros(-router.shape[0] % 8, router.shape[1])], dim=0)
+        self.w_router = runtime.matrix(router)
         self.w_up = runtime.matrix(torch.cat([t for n in names for t in (tensors[f"{n}.gate"], tensors[f"{n}.up"])], dim=0))
         self.w_down = runtime.matrix(torch.cat([tensors[f"{n}.down"] for n in names], dim=1))
         routed_rows, routed_cols = 2 * spec.experts * spec.expert_ff, spec.experts * spec.expert_ff
@@ -73,7 +79,7 @@ class GroupedRoutedMLP:
 
     def _route(self, x, chosen=None):
         s = self.spec
-        logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
+        logits = ops.linear(x, self.w_router, out_dtype=torch.float32)[:, :self.router_rows]
         return ops.route_grouped(logits, s.experts, s.top, s.groups, s.keep_groups, s.group_top, s.route_scale, chosen=chosen)
 
     def _sorted_forward(self, x):

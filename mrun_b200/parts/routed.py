@@ -16,8 +16,10 @@ in that order, both products run as grouped products over the experts' row range
 the row's weight between them, and one kernel adds each token's rows, in the order its experts
 were chosen, to the shared expert's output.  Smaller steps, and the 32-bit path, compute every
 expert with zero weights as above: the sort, the gather and the grouped products' set-up cost a few
-hundred microseconds of a step (measured on B200: at 2,048 rows, width 2,048 and 8 experts of
-2,048 of which 2 are chosen the sorted step loses, at width 4,096 and experts of 3,072 it wins),
+hundred microseconds of a step (measured on B200 at 2,048 rows and 8 experts of which 2 are
+chosen: at width 2,048 and experts of 2,048 the sorted step loses 3 % with two products an
+expert, 2.1e11 FLOPs saved, and wins 8 to 10 % with three, 3.1e11; at width 4,096 and experts of
+3,072 it wins 12 % with two),
 with a handful of rows most experts' weights are read either way, and the 32-bit path keeps one
 summation order for every cutting.  ``MRUN_MOE_SORT_MIN_FLOPS`` in the environment overrides the
 threshold (0: every bfloat16 step sorts).
@@ -34,7 +36,7 @@ from .base import Runtime, register_feed_forward
 
 ACTIVATIONS = ("relu2",)
 # FLOPs a step would spend on experts nobody chose, from which its pairs are sorted by expert
-SORT_MIN_SAVED_FLOPS = float(os.environ.get("MRUN_MOE_SORT_MIN_FLOPS", 4e11))
+SORT_MIN_SAVED_FLOPS = float(os.environ.get("MRUN_MOE_SORT_MIN_FLOPS", 2.5e11))
 
 
 @register_feed_forward("routed_mlp")
