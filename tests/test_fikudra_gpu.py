@@ -777,3 +777,63 @@ def test_command_line_random_then_run(tmp_path):
         assert token == best or float(logits[best] - logits[token]) < 1e-3
         tokens.append(token)
     assert len(tokens) == 19 + 6 and "Fikudra" in result.stderr
+
+
+# ------------------------------------------------------------------ layer sizes of a real model
+
+REAL_MOE = {"kind": "moe", "router": {"experts": 8, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+            "expert": {"ff": 512}, "shared": {"ff": 512}}
+REAL_ATTENTION = {"heads": 8, "kv_heads": 2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                  "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 2.0}}}
+REAL_SIZES = {"architecture": "Fikudra", "vocab": 4096, "width": 1024, "norm": {"eps": 1e-6}, "streams": 4,
+              "embedding": {"scale": 4.0, "bigram": {"buckets": 1021, "mul_prev": 1000003, "mul_cur": 7}},
+              "layers": [{"type": "attention", "mixer": REAL_ATTENTION, "mlp": REAL_MOE},
+                         {"type": "gla", "mixer": {"heads": 8, "dim": 128, "vdim": 128, "tau": 8.0, "rank": 64}, "mlp": REAL_MOE},
+                         {"type": "attention", "mixer": dict(REAL_ATTENTION, kv_from=0), "mlp": None}]}
+
+
+@pytest.mark.parametrize("dtype, sorted_experts, top", [("float32", False, 2), ("bfloat16", False, 8), ("bfloat16", True, 2)])
+def test_real_layer_sizes(dtype, sorted_experts, top, tmp_path, monkeypatch):
+    """Heads of 128 x 128 (full row slices of the scan; in bfloat16 the tcgen05 and TMA attention
+    kernels with the sink and the head gate in 16-byte steps), four streams of 1,024, eight experts
+    of 512 in four groups with a shared one, a router product padded to 16 rows: a prompt whole and
+    in portions, then decoded token by token, against the plain model.  With two experts chosen a
+    bfloat16 run is held to the bound where no choice up to the position was a close call, and at
+    seven in ten of all positions; with every expert chosen (all groups kept) at every position."""
+    import copy
+    from mrun_b200.config.fikudra import FikudraConfig
+    from mrun_b200.engine import StepEntry
+    from mrun_b200.engine.loading import executor_from_folder
+    from mrun_b200.parts import routed
+    from mrun_b200.weights import write_random_model
+    monkeypatch.setattr(routed, "SORT_MIN_SAVED_FLOPS", 0.0 if sorted_experts else 1e30)
+    sizes = copy.deepcopy(REAL_SIZES)
+    for entry in sizes["layers"]:
+        if entry["mlp"] is not None:
+            entry["mlp"]["router"]["top"] = top
+            entry["mlp"]["router"]["groups"]["keep"] = 2 if top == 2 else 4
+    folder = write_random_model(FikudraConfig.from_dict(sizes), str(tmp_path / "real"), seed=7, std=0.03, norm_noise=0.1)
+    cfg, weights = load_folder(folder)
+    tokens = tokens_of(cfg["vocab"], 330, seed=77)
+    margins = []
+    want = plain.forward(cfg, weights, tokens, margins=margins).to(torch.float32)
+    sure = torch.from_numpy(~close_calls(margins, len(tokens))) if dtype == "bfloat16" else torch.ones(330, dtype=torch.bool)
+    ex = executor_from_folder(folder, dtype=dtype, page_size=16, num_pages=64, max_requests=2)
+    seen = {}
+    for label, portions in (("whole", [330]), ("portions", [200, 3, 65, 30] + [1] * 32)):
+        request, at, got = ex.admit(label), 0, []
+        for n in portions:
+            got.append(ex.step([StepEntry(request, tokens[at:at + n], list(range(n)))]).cpu())
+            at += n
+        ex.release(request)
+        got = torch.cat(got)
+        errors = (got - want).abs().max(1).values / want.abs().max()
+        print(dtype, sorted_experts, label, f"{float(errors[sure].max()):.2e} at the {int(sure.sum())} sure positions, "
+              f"{float(errors.max()):.2e} at all")
+        if dtype == "float32":
+            assert float(errors.max()) <= 2e-5, f"{label}: {float(errors.max()):.3e}"
+            assert torch.equal(seen.setdefault("logits", got), got), "the cuttings differ in bits"
+        else:
+            assert int(sure.sum()) >= (5 if top == 2 else 330) and float(errors[sure].max()) <= 4e-2, f"{label}: {float(errors[sure].max()):.3e}"
+            assert int((errors <= 4e-2).sum()) >= 0.7 * len(tokens), f"{label}: {int((errors <= 4e-2).sum())} of {len(tokens)} within the bound"
+    ex.check()

@@ -105,6 +105,21 @@ FTINY = {
                                  {"kind": "dense", "ff": 48}),
                            layer("gla", gla(2, 16, 48, 2.0, 4), None)]},
         seed=21, std=0.1, norm_noise=0.2, page_size=16),
+    # six layers with two page owners of different sizes, each read by a later layer, the readers in
+    # the other order than the owners; a linear attention first and last, one with a single head as
+    # wide as the model; one expert chosen of two; nine experts in three groups; a table of two rows
+    "U": dict(
+        config={"architecture": "Fikudra", "vocab": 90, "width": 48, "norm": {"eps": 1e-6}, "streams": 2,
+                "embedding": {"scale": 4.0, "bigram": {"buckets": 2, "mul_prev": 5, "mul_cur": 3}},
+                "layers": [layer("gla", gla(2, 8, 12, 1.5, 2), moe(2, 1, 8)),
+                           layer("attention", attention(2, 2, 32, 32, 0.2, rot_dims=16, base=1000.0), None),
+                           layer("attention", attention(4, 1, 16, 8, 0.3, rot_dims=16, base=50.0, factor=3.0),
+                                 moe(9, 3, 8, groups=3, keep=2, scale=0.7, shared=8)),
+                           layer("attention", attention(4, 1, 16, 8, 0.25, rot_dims=16, base=50.0, factor=3.0, kv_from=2),
+                                 {"kind": "dense", "ff": 32}),
+                           layer("attention", attention(2, 2, 32, 32, 0.2, rot_dims=16, base=1000.0, kv_from=1), None),
+                           layer("gla", gla(1, 48, 48, 64.0, 3), moe(4, 2, 8, shared=4))]},
+        seed=33, std=0.15, norm_noise=0.2, page_size=8),
 }
 
 
