@@ -110,6 +110,8 @@ class FikudraConfig:
             raise ConfigError(f"{where}mlp", "is neither an object nor null")
         fw = f"{where}mlp."
         kind = mlp.get("kind")
+        if kind is None:        # left out: what the entry holds says which it is
+            kind = "moe" if "router" in mlp else "dense" if "ff" in mlp else None
         if kind == "dense":
             return GatedMLPSpec(width, _count(mlp, "ff", fw), "silu", tensor_names=("gate", "up", "down"))
         if kind != "moe":

@@ -133,6 +133,14 @@ def test_defaults_of_keys_a_config_may_leave_out():
     spec = config.to_spec()
     assert spec.streams == 1 and all(l.streams == 0 for l in spec.layers)
     assert spec.layers[2].feed_forward_norm is None
+    # a feed-forward entry without "kind" is what its keys say
+    from mrun_b200.config.fikudra import FikudraConfig
+    cfg = copy.deepcopy(FTINY["Q"]["config"])
+    for entry in cfg["layers"]:
+        if entry["mlp"] is not None:
+            entry["mlp"].pop("kind")
+    again = FikudraConfig.from_dict(cfg)
+    assert [type(l.feed_forward) for l in again.layers] == [type(l.feed_forward) for l in config.layers]
 
 
 def test_random_folder_and_rank_from_the_checkpoint(tmp_path):
