@@ -51,6 +51,17 @@ class RMSNormSpec:
     offset: float = 0.0
 
 
+@dataclass(frozen=True)
+class LayerNormSpec:
+    """Layer norm with a weight and no bias: (x - mean) / sqrt(variance + eps) * w, the variance
+    the mean of the squared deviations.  ``bare`` as for :class:`RMSNormSpec`."""
+
+    kind: ClassVar[str] = "layernorm"
+    size: int
+    eps: float
+    bare: bool = False
+
+
 # --------------------------------------------------------------------------- position encodings
 
 @dataclass(frozen=True)
@@ -110,11 +121,13 @@ class LatentAttentionSpec:
     """Softmax attention whose keys and values are up-projections of one cached latent per token.
 
     Per token: the query goes through a latent of ``q_rank`` features (RMS-normed), then up to
-    ``heads`` heads of ``dim`` plain and ``rot_dim`` rotated features.  One down-projection gives
+    ``heads`` heads of ``dim`` plain and ``rot_dim`` rotated features (``q_rank`` = 0: one
+    projection ``q`` straight from the input, no latent and no norm).  One down-projection gives
     the key/value latent of ``kv_rank`` features (RMS-normed) and ``rot_dim`` more that are the
     rotated key part all heads share.  A head's plain key is an up-projection of the latent, its
     value (``vdim`` features) another; the score is (plain . plain + rotated . rotated) *
-    ``softmax_scale``.  The cache holds the latent and the shared rotated part only."""
+    ``softmax_scale``.  The cache holds the latent and the shared rotated part only.  ``window``
+    = W: a token sees the last W keys, itself included."""
 
     kind: ClassVar[str] = "latent_attention"
     hidden: int
@@ -127,6 +140,7 @@ class LatentAttentionSpec:
     softmax_scale: float
     eps: float
     position: Optional[Any] = None
+    window: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -155,14 +169,20 @@ class DifferentialAttentionSpec:
 @dataclass(frozen=True)
 class GatedAttentionSpec:
     """Grouped-query softmax attention whose keys (``dim`` a head) and values (``vdim`` a head)
-    may differ in size, with three options.  ``qk_norm`` = ``"projection"``: q and k are each
+    may differ in size, with these options.  ``qk_norm`` = ``"projection"``: q and k are each
     divided by the root mean square over the whole projection (all heads together, ``eps`` inside
-    the root) and multiplied by a weight of that size, before the rotation; None: no norm.
+    the root) and multiplied by a weight of that size, before the rotation; ``"head"``: every head
+    is divided by its own root mean square over ``dim`` and multiplied by a weight of ``dim``
+    entries that the heads share; None: no norm.
     ``sink``: the softmax has one more term of score 0 and no value, p_j = exp(s_j) / (1 + sum
     exp(s)).  ``head_gate``: head h's output is multiplied by sigmoid(g x)_h, one projection row a
     head.  ``own_kv`` False: the layer has no key and value projections and reads the pages of
     another schedule entry (``ScheduleEntry.cache_of``), with queries, gate and output of its
-    own."""
+    own.  ``values`` = ``"keys"``: there is no value projection and the values are the keys as
+    they come out of their projection, before norm and rotation (``vdim`` = ``dim``).  Which keys a
+    token at position i sees: all up to itself; with ``window`` = W the last W, itself included;
+    with ``chunk`` = C those of its own chunk, floor(j / C) = floor(i / C), chunks counted from
+    position 0 of the sequence."""
 
     kind: ClassVar[str] = "gated_attention"
     hidden: int
@@ -178,6 +198,8 @@ class GatedAttentionSpec:
     own_kv: bool = True
     position: Optional[Any] = None
     window: Optional[int] = None
+    chunk: Optional[int] = None
+    values: str = "projection"
 
 
 @dataclass(frozen=True)
@@ -239,6 +261,24 @@ class ChannelDeltaSpec:
     eps: float
 
 
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers side by side that read the same input: the result is ``share`` times the sum of
+    their outputs, each first divided by its root mean square over the model width (``eps``
+    inside the root) and multiplied by a weight of its own, ``<left_prefix>.<out_name>`` and
+    ``<right_prefix>.<out_name>``.  The two may keep a cache each, at most one of them paged."""
+
+    kind: ClassVar[str] = "parallel"
+    hidden: int
+    left: Any
+    right: Any
+    eps: float
+    share: float = 0.5
+    left_prefix: str = "left"
+    right_prefix: str = "right"
+    out_name: str = "out"
+
+
 # --------------------------------------------------------------------------- feed-forwards
 
 @dataclass(frozen=True)
@@ -252,6 +292,20 @@ class GatedMLPSpec:
     # the checkpoint's names of the gate, up and down matrices under the part's prefix; a name
     # that ends in ``.weight`` may have a ``.bias`` beside it
     tensor_names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
+
+@dataclass(frozen=True)
+class ClampedGatedMLPSpec:
+    """A dense gated feed-forward with clamped branches: g = min(gate x, limit), u = clamp(up x,
+    -limit, limit), y = g * sigmoid(alpha * g) * (u + 1), output down y.  ``biases``: every
+    projection has a bias ``<name>.b``."""
+
+    kind: ClassVar[str] = "clamped_gated_mlp"
+    hidden: int
+    intermediate: int
+    limit: float
+    alpha: float = 1.702
+    biases: bool = True
 
 
 @dataclass(frozen=True)
@@ -282,7 +336,9 @@ class GroupedRoutedMLPSpec:
     Each token takes the ``top`` allowed experts with the largest scores; their weights are the
     scores divided by their sum (+ 1e-20) times ``route_scale``.  ``shared_ff`` > 0: one more
     expert of that size runs for every token, weighed by sigmoid(sg x) (one number a token) when
-    ``shared_gate``, else by 1."""
+    ``shared_gate``, else by 1.  ``score`` = ``"logit"`` (without groups): the router's logits
+    themselves are ranked, and the chosen experts weigh the softmax over the chosen logits only.
+    ``router_bias``: the router has a bias ``router.b`` added to its logits."""
 
     kind: ClassVar[str] = "grouped_routed_mlp"
     hidden: int
@@ -296,6 +352,8 @@ class GroupedRoutedMLPSpec:
     shared_ff: int = 0
     shared_gate: bool = True
     activation: str = "silu"
+    score: str = "sigmoid"
+    router_bias: bool = False
 
 
 @dataclass(frozen=True)

@@ -165,7 +165,7 @@ __device__ __forceinline__ Segment next_segment(int seg, int u, int u_end, int& 
     sg.complete = sg.j0 == 0 && sg.len == sg.pair_tiles;
     sg.pair_start = kvh * tiles_per_head + prefix[tok];
     sg.pos = positions[tok];
-    sg.lo = (window > 0 && sg.pos - window + 1 > 0) ? sg.pos - window + 1 : 0;
+    sg.lo = mrun::first_visible(sg.pos, window);
     sg.first_block = sg.lo / BLOCK_N + sg.j0;
     sg.last_block = sg.first_block + sg.len - 1;
     return sg;
@@ -566,7 +566,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                 out[((size_t)q_row * heads + kvh * group) * D + i] = __float2bfloat16_rn(0.f);
         return;
     }
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = mrun::first_visible(pos, window);
     const int b0 = lo / BLOCK_N, b1 = pos / BLOCK_N, pair_tiles = b1 - b0 + 1;
     const int base = pair_tiles / (int)pieces, extra = pair_tiles - base * (int)pieces;
     const int len = base + ((int)rank < extra ? 1 : 0);

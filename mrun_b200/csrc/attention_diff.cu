@@ -96,7 +96,7 @@ diff_attention_kernel(const TA* __restrict__ q, long q_stride, TA* __restrict__ 
     const size_t map_stride = (size_t)pages * G * page_size * D;
     const size_t chunk_stride = (size_t)pages * G * page_size * Dv;
 
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = first_visible(pos, window);
     float m1 = -INFINITY, l1 = 0.f, m2 = -INFINITY, l2 = 0.f;
     float acc1[8], acc2[8];  // V <= 8 * THREADS
 #pragma unroll
@@ -237,7 +237,7 @@ MRUN_API int mrun_diff_attention(const void* q, long q_stride, void* out, const 
     MRUN_REQUIRE(D <= 4096, "diff_attention: key size %d exceeds the supported 4096", D);
     MRUN_REQUIRE(H <= 65535, "diff_attention: heads=%d exceeds 65535", H);
     MRUN_REQUIRE(pages * G * page_size < (1L << 31), "diff_attention: the cache has too many rows");
-    MRUN_REQUIRE(window >= 0, "diff_attention: window=%d is negative", window);
+    MRUN_REQUIRE(window >= 0, "diff_attention: window=%d is negative (this attention has no chunked form)", window);
     if (tokens == 0) return 0;
     const dim3 grid(tokens, H);
     const size_t smem = (size_t)(2 * D + 3 * THREADS) * sizeof(float);

@@ -151,7 +151,7 @@ inline int check_common(const char* name, int heads, int kv_heads, int head_dim,
                  "%s: heads=%d must be a positive multiple of kv_heads=%d", name, heads, kv_heads);
     MRUN_REQUIRE(heads / kv_heads <= max_group, "%s: %d query heads per kv head exceed the supported %d", name,
                  heads / kv_heads, max_group);
-    MRUN_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "%s: bad page_size/max_blocks/window", name);
+    MRUN_REQUIRE(page_size > 0 && max_blocks > 0, "%s: bad page_size/max_blocks", name);
     MRUN_REQUIRE(kv_heads <= 65535, "%s: kv_heads=%d exceeds 65535", name, kv_heads);
     return 0;
 }

@@ -50,7 +50,7 @@ paged_attention_generic_kernel(const TA* __restrict__ q, long q_stride, TA* __re
     for (int d = tid; d < head_dim; d += THREADS) qs[d] = to_float(qrow[d]);
     __syncthreads();
 
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = first_visible(pos, window);
     float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
     float acc[8];  // value_dim <= 8 * THREADS = 1024
 #pragma unroll
@@ -124,7 +124,6 @@ MRUN_API int mrun_paged_attention_generic(const void* q, long q_stride, void* ou
     MRUN_REQUIRE(heads <= 65535, "paged_attention_generic: heads=%d exceeds 65535", heads);
     MRUN_REQUIRE(cache_rows < (1L << 31), "paged_attention_generic: the cache has %ld rows, the limit is 2^31",
                  cache_rows);
-    MRUN_REQUIRE(window >= 0, "paged_attention_generic: window=%d is negative", window);
     if (tokens == 0) return 0;
     const dim3 grid(tokens, heads);
     const size_t smem = (size_t)(head_dim + 2 * THREADS) * sizeof(float);

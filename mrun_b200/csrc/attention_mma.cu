@@ -171,7 +171,7 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
 
     // tokens of a tile are consecutive positions of one request
     const int pos_first = positions[tok0], pos_last = pos_first + ntok - 1;
-    const int lo_tile = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const int lo_tile = mrun::first_visible(pos_first, window);
     const int first_block = lo_tile / BLOCK_N, last_block = pos_last / BLOCK_N;
 
     // q rows: row r = (token r / group, head kvh * group + r % group)
@@ -192,7 +192,7 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
     for (int r = 0; r < 2; ++r) {
         const int row = warp * 16 + (lane >> 2) + r * 8;
         row_pos[r] = row < n_rows ? pos_first + row / group : -1;
-        row_lo[r] = (window > 0 && row_pos[r] - window + 1 > 0) ? row_pos[r] - window + 1 : 0;
+        row_lo[r] = mrun::first_visible(row_pos[r], window);
     }
     // the warp's rows span tokens [w_first, w_last]: blocks above w_last's position are skipped
     const int w_row0 = warp * 16;
@@ -218,10 +218,10 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
         __syncthreads();
         const int key_base = block * BLOCK_N;
         if (warp_active && key_base <= w_pos_last) {
-            const int w_lo = (window > 0 && w_pos_first - window + 1 > 0) ? w_pos_first - window + 1 : 0;
+            const int w_lo = mrun::first_visible(w_pos_first, window);
             if (key_base + BLOCK_N - 1 >= w_lo) {
                 // full visibility for every row of the warp needs no mask
-                const int w_lo_last = (window > 0 && w_pos_last - window + 1 > 0) ? w_pos_last - window + 1 : 0;
+                const int w_lo_last = mrun::first_visible(w_pos_last, window);
                 const bool need_mask = key_base + BLOCK_N - 1 > w_pos_first || key_base < w_lo_last;
                 attend_tile<BLOCK_N>(q_tile + w_row0 * LD, k_tiles + stage * BLOCK_N * LD,
                                      v_tiles + stage * BLOCK_N * LD, 0, key_base, scale_log2, need_mask, row_pos,
@@ -338,7 +338,7 @@ __global__ void decode_plan_kernel(const int* __restrict__ positions, int tokens
     plan_prefix([&](int t) {
         const int pos = positions[t];
         if (pos < 0) return 0;
-        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int lo = mrun::first_visible(pos, window);
         return pos / BLOCK_N - lo / BLOCK_N + 1;
     }, tokens, tile_prefix, scan, &carry);
     if (blocks_per_head <= 0) return;
@@ -473,7 +473,7 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
 
         const int pos = positions[tok];
         const Paging pg{block_tables + (size_t)token_slot[tok] * max_blocks, kv_heads, kvh, page_size, page_shift};
-        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int lo = mrun::first_visible(pos, window);
         const int b1 = pos / BLOCK_N;
         const int first_block = lo / BLOCK_N + j0;
         const int last_block = first_block + len - 1;
@@ -740,7 +740,7 @@ MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const vo
 MRUN_API int mrun_attn_decode_plan(const int* positions, int tokens, int window, int kv_heads, int blocks,
                                    int min_tiles, int splits, int* tile_prefix, int* assignment,
                                    cudaStream_t stream) {
-    MRUN_REQUIRE(tokens >= 0 && window >= 0 && kv_heads >= 1 && blocks >= 1 && min_tiles >= 1 && splits >= 0,
+    MRUN_REQUIRE(tokens >= 0 && kv_heads >= 1 && blocks >= 1 && min_tiles >= 1 && splits >= 0,
                  "attn_decode_plan: tokens=%d window=%d kv_heads=%d blocks=%d min_tiles=%d splits=%d", tokens, window,
                  kv_heads, blocks, min_tiles, splits);
     MRUN_REQUIRE(splits == 0 || (blocks % kv_heads == 0 && blocks / kv_heads >= tokens),

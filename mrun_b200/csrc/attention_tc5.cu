@@ -137,7 +137,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     const int n_rows = ntok * group;
     // tokens of a tile are consecutive positions of one request
     const int pos_first = positions[tok0], pos_last = pos_first + ntok - 1;
-    const int lo_tile = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const int lo_tile = mrun::first_visible(pos_first, window);
     const int first_block = lo_tile / KEYS, last_block = pos_last / KEYS;
     const int n_tiles = last_block - first_block + 1;
 
@@ -188,9 +188,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         if (lane == 0) mbar_arrive(&bars.q_full);
 
         const int row_pos = row < n_rows ? pos_first + row / group : -1;      // -1: padding row
-        const int row_lo = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
+        const int row_lo = mrun::first_visible(row_pos, window);
         // the tile's last row sees the most recent keys, its first row the oldest
-        const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
+        const int lo_last = mrun::first_visible(pos_last, window);
         float m_used = -INFINITY, l = 0.f;                           // l: this half's share of the row's sum
         bool alive = true;
         // A warp that gave up on a wait still walks through the remaining tiles, doing nothing but
@@ -464,7 +464,7 @@ MRUN_API int mrun_attn_prefill_tc5(const void* q, long q_stride, void* out, cons
                  "attn_prefill_tc5: heads=%d must be a positive multiple of kv_heads=%d", heads, kv_heads);
     MRUN_REQUIRE(heads / kv_heads <= ROWS, "attn_prefill_tc5: %d query heads per kv head exceed the supported %d",
                  heads / kv_heads, ROWS);
-    MRUN_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attn_prefill_tc5: bad page_size/max_blocks/window");
+    MRUN_REQUIRE(page_size > 0 && max_blocks > 0, "attn_prefill_tc5: bad page_size/max_blocks");
     MRUN_REQUIRE(n_tiles >= 0, "attn_prefill_tc5: n_tiles=%d", n_tiles);
     MRUN_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
                  ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,

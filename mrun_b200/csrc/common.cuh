@@ -122,6 +122,15 @@ template <> struct Vec8<__nv_bfloat16> {
     }
 };
 
+// The first key a token at position `pos` sees.  window = 0: every key from the start; window =
+// W > 0: the last W keys, itself included; window = -C < 0: the keys of its own chunk, chunks of
+// C positions counted from position 0 of the sequence.  Monotone in `pos` in all three forms.
+__host__ __device__ __forceinline__ int first_visible(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos < 0 ? 0 : pos - pos % (-window);
+    return 0;
+}
+
 // Sum over a warp in a fixed butterfly order: every lane gets the same bits.
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -750,3 +750,112 @@ MRUN_API int mrun_head_gate(void* y, const void* gate, long ldg, int act_dtype, 
     MRUN_CHECK_LAUNCH("head_gate");
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------
+// Per-head RMS norm of q and k (one weight of `dim` entries that the heads share, eps inside the
+// root), rotation of the first `rotary_dim` features of every head in either pairing, k and v into
+// the pages, for rows whose q, k and v heads start at columns of their own (q_off, k_off, v_off)
+// and whose keys (`dim` a head) and values (`vdim` a head) may differ in size.
+//   v_off < 0: the layer has no value projection and the values are the keys as they were
+//   projected, before the norm and the rotation (vdim = dim).
+// q is worked on in place; a negative slot skips the page writes.  One warp per (token, q or k
+// or v head); the head's vector is staged in shared memory in 32-bit.
+// ------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void head_norm_rope_cache_kernel(TA* __restrict__ x, long ld, long q_off, long k_off, long v_off,
+                                            const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                            float eps, const float2* __restrict__ rot, int rotary_dim, int interleaved,
+                                            const int* __restrict__ slots, TA* __restrict__ k_cache,
+                                            TA* __restrict__ v_cache, int tokens, int heads, int kv_heads, int dim,
+                                            int vdim, int page_size) {
+    extern __shared__ float vec_buf[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per_token = heads + (v_off >= 0 ? 2 : 1) * kv_heads;
+    const long item = (long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long)tokens * per_token) return;
+    const int t = (int)(item / per_token), slot_head = (int)(item - (long)t * per_token);
+    const bool is_q = slot_head < heads;
+    const bool is_k = !is_q && slot_head < heads + kv_heads;
+    const int slot = slots ? slots[t] : -1;
+    if (!is_q && slot < 0) return;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
+    TA* row = x + (size_t)t * ld;
+    if (!is_q && !is_k) {       // a value head of a projection of its own: plain copy
+        const int g = slot_head - heads - kv_heads;
+        const TA* src = row + v_off + (size_t)g * vdim;
+        TA* dst = v_cache + (((size_t)page * kv_heads + g) * page_size + off) * vdim;
+        for (int e = lane; e < vdim; e += 32) dst[e] = src[e];
+        return;
+    }
+    const int g = is_q ? slot_head : slot_head - heads;
+    TA* src = row + (is_q ? q_off : k_off) + (size_t)g * dim;
+    TA* dst = is_q ? src : k_cache + (((size_t)page * kv_heads + g) * page_size + off) * dim;
+    float* vec = vec_buf + warp * dim;
+    float ss = 0.f;
+    for (int e = lane; e < dim; e += 32) {
+        const float v = to_float(src[e]);
+        vec[e] = v;
+        ss += v * v;
+    }
+    if (is_k && v_off < 0) {    // the values are the keys as projected
+        TA* vdst = v_cache + (((size_t)page * kv_heads + g) * page_size + off) * vdim;
+        for (int e = lane; e < dim; e += 32) vdst[e] = src[e];
+    }
+    const float* weight = is_q ? q_weight : k_weight;
+    if (weight) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)dim + eps);
+        __syncwarp();
+        for (int e = lane; e < dim; e += 32) vec[e] = vec[e] * inv * weight[e];
+    }
+    __syncwarp();
+    const int half = rotary_dim >> 1;
+    if (rot && half > 0) {
+        const float2* cs = rot + (size_t)t * half;
+        for (int j = lane; j < half; j += 32) {
+            const int a = interleaved ? 2 * j : j, b = interleaved ? 2 * j + 1 : j + half;
+            const float x1 = vec[a], x2 = vec[b];
+            const float2 c = cs[j];
+            dst[a] = from_float<TA>(x1 * c.x - x2 * c.y);
+            dst[b] = from_float<TA>(x2 * c.x + x1 * c.y);
+        }
+        for (int e = rotary_dim + lane; e < dim; e += 32) dst[e] = from_float<TA>(vec[e]);
+    } else {
+        for (int e = lane; e < dim; e += 32) dst[e] = from_float<TA>(vec[e]);
+    }
+}
+
+MRUN_API int mrun_head_norm_rope_cache(void* x, long ld, long q_off, long k_off, long v_off, int act_dtype,
+                                       const float* q_weight, const float* k_weight, float eps, const float* rot,
+                                       int rotary_dim, int pairing, const int* slots, void* k_cache, void* v_cache,
+                                       int tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
+                                       cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && page_size > 0,
+                 "head_norm_rope_cache: bad sizes tokens=%d heads=%d kv_heads=%d dim=%d vdim=%d page_size=%d", tokens,
+                 heads, kv_heads, dim, vdim, page_size);
+    MRUN_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= dim,
+                 "head_norm_rope_cache: rotary_dim=%d must be even and at most dim=%d", rotary_dim, dim);
+    MRUN_REQUIRE(pairing == 0 || pairing == 1, "head_norm_rope_cache: unknown pairing code %d", pairing);
+    MRUN_REQUIRE(v_off >= 0 || vdim == dim, "head_norm_rope_cache: values that are the keys have the keys' size (%d), not %d",
+                 dim, vdim);
+    MRUN_REQUIRE(q_off >= 0 && k_off >= 0, "head_norm_rope_cache: negative column of q or k");
+    MRUN_REQUIRE((size_t)dim * sizeof(float) * 4 <= 48 * 1024, "head_norm_rope_cache: dim=%d exceeds the supported 3072", dim);
+    if (tokens == 0) return 0;
+    const int warps = 4;
+    const long items = (long)tokens * (heads + (v_off >= 0 ? 2 : 1) * kv_heads);
+    const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+    const size_t smem = (size_t)warps * dim * sizeof(float);
+    if (slots == nullptr) k_cache = v_cache = nullptr;
+    if (act_dtype == MRUN_F32)
+        head_norm_rope_cache_kernel<float><<<blocks, warps * 32, smem, stream>>>(
+            (float*)x, ld, q_off, k_off, v_off, q_weight, k_weight, eps, (const float2*)rot, rotary_dim, pairing, slots,
+            (float*)k_cache, (float*)v_cache, tokens, heads, kv_heads, dim, vdim, page_size);
+    else if (act_dtype == MRUN_BF16)
+        head_norm_rope_cache_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+            (__nv_bfloat16*)x, ld, q_off, k_off, v_off, q_weight, k_weight, eps, (const float2*)rot, rotary_dim, pairing,
+            slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens, heads, kv_heads, dim, vdim, page_size);
+    else
+        return mrun_set_error("head_norm_rope_cache: unknown dtype code %d", act_dtype);
+    MRUN_CHECK_LAUNCH("head_norm_rope_cache");
+    return 0;
+}

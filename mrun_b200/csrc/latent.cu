@@ -80,13 +80,13 @@ latent_prepare_kernel(const TA* __restrict__ down, long ld, const float* __restr
 // ------------------------------------------------------------------------------------------
 template <typename TA>
 __global__ void __launch_bounds__(256)
-latent_query_kernel(const TA* __restrict__ q, const float2* __restrict__ rot, int rot_dims, int interleaved,
+latent_query_kernel(const TA* __restrict__ q, long ldq, const float2* __restrict__ rot, int rot_dims, int interleaved,
                     TA* __restrict__ q_att, int heads, int dim, int rot_dim, int kv_rank, int width) {
     const int t = blockIdx.x;
     const int pairs = rot_dims / 2, tail = width - kv_rank;
     for (int item = threadIdx.x; item < heads * tail; item += blockDim.x) {
         const int h = item / tail, j = item - h * tail;
-        const TA* src = q + ((size_t)t * heads + h) * (dim + rot_dim) + dim;
+        const TA* src = q + (size_t)t * ldq + (size_t)h * (dim + rot_dim) + dim;
         TA* dst = q_att + ((size_t)t * heads + h) * width + kv_rank;
         if (j >= rot_dim) { dst[j] = from_float<TA>(0.f); continue; }
         if (j >= rot_dims) { dst[j] = src[j]; continue; }
@@ -201,31 +201,37 @@ post_norm_add_vec_kernel(float* __restrict__ stream, const float* __restrict__ b
 }
 
 // ------------------------------------------------------------------------------------------
-// Router: one warp a token.  score = softmax over all experts (kind 0) or a sigmoid of each
-// logit (kind 1); the `top` largest scores are chosen (the smaller index wins a tie); the
-// output row holds the chosen experts' scores, divided by their sum if `renormalize`, and zero
-// elsewhere.  `chosen` (nullable) gets the expert ids in the order they were picked.
+// Router: one warp a token.  score = softmax over all experts (kind 0), a sigmoid of each
+// logit (kind 1) or the logit itself (kind 2); the `top` largest scores are chosen (the smaller
+// index wins a tie); the output row holds the chosen experts' scores, divided by their sum if
+// `renormalize`, and zero elsewhere; with kind 2 it holds the softmax over the chosen logits
+// only.  `bias` (nullable, one entry an expert) is added to the logits first; a row of logits
+// starts `ldz` entries after the one before.  `chosen` (nullable) gets the expert ids in the
+// order they were picked.
 // ------------------------------------------------------------------------------------------
 constexpr int ROUTE_MAX_PER_LANE = 16;      // experts <= 512
 
 // PER_LANE: experts a lane holds (experts <= 32 * PER_LANE)
 template <int PER_LANE>
 __global__ void __launch_bounds__(128)
-route_top_k_kernel(const float* __restrict__ logits, float* __restrict__ weights, int* __restrict__ chosen,
-                   int tokens, int experts, int top, int kind, int renormalize) {
+route_top_k_kernel(const float* __restrict__ logits, long ldz, const float* __restrict__ bias,
+                   float* __restrict__ weights, int* __restrict__ chosen, int tokens, int experts, int top, int kind,
+                   int renormalize) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= tokens) return;
-    const float* z = logits + (size_t)t * experts;
+    const float* z = logits + (size_t)t * ldz;
     float s[PER_LANE];
     float m = -INFINITY;
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) {
         const int e = lane + 32 * i;
-        s[i] = e < experts ? z[e] : -INFINITY;
+        s[i] = e < experts ? z[e] + (bias ? bias[e] : 0.f) : -INFINITY;
         m = fmaxf(m, s[i]);
     }
-    if (kind == 0) {
+    if (kind == 2) {
+        // the logits themselves are the scores
+    } else if (kind == 0) {
         m = warp_max(m);
         float sum = 0.f;
 #pragma unroll
@@ -249,19 +255,26 @@ route_top_k_kernel(const float* __restrict__ logits, float* __restrict__ weights
     float total = 0.f;
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) w[i] = 0.f;
+    float first = 0.f;          // kind 2: the largest chosen logit, which the exponentials are taken against
     for (int k = 0; k < top; ++k) {
-        float best = -1.f;
+        float best = kind == 2 ? -INFINITY : -1.f;
         int best_e = 0x7fffffff;
 #pragma unroll
         for (int i = 0; i < PER_LANE; ++i) {
             const int e = lane + 32 * i;
-            if (e < experts && !(taken >> i & 1u) && s[i] > best) { best = s[i]; best_e = e; }
+            if (e < experts && !(taken >> i & 1u) && (s[i] > best || (best_e == 0x7fffffff && s[i] == best))) {
+                best = s[i]; best_e = e;
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
             const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
             if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (kind == 2) {
+            if (k == 0) first = best;
+            best = expf(best - first);
         }
         if ((best_e & 31) == lane) {
             const int i = best_e >> 5;
@@ -272,7 +285,7 @@ route_top_k_kernel(const float* __restrict__ logits, float* __restrict__ weights
         total += best;
         if (chosen && lane == 0) chosen[(size_t)t * top + k] = best_e;
     }
-    const float norm = renormalize ? 1.f / total : 1.f;
+    const float norm = (renormalize || kind == 2) ? 1.f / total : 1.f;
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) {
         const int e = lane + 32 * i;
@@ -356,7 +369,7 @@ MRUN_API int mrun_latent_prepare(const void* down, int act_dtype, long ld, const
     return 0;
 }
 
-MRUN_API int mrun_latent_query(const void* q, int act_dtype, const float* rot, int rot_dims, int interleaved,
+MRUN_API int mrun_latent_query(const void* q, long ldq, int act_dtype, const float* rot, int rot_dims, int interleaved,
                                void* q_att, int tokens, int heads, int dim, int rot_dim, int kv_rank, int width,
                                cudaStream_t stream) {
     MRUN_REQUIRE(tokens >= 0 && heads > 0 && dim >= 0 && rot_dim >= 0 && kv_rank > 0 && width >= kv_rank + rot_dim,
@@ -365,14 +378,15 @@ MRUN_API int mrun_latent_query(const void* q, int act_dtype, const float* rot, i
     MRUN_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= rot_dim,
                  "latent_query: %d rotating features of %d", rot_dims, rot_dim);
     MRUN_REQUIRE(rot_dims == 0 || rot != nullptr, "latent_query: no rotation table");
+    MRUN_REQUIRE(ldq >= (long)heads * (dim + rot_dim), "latent_query: rows of %ld entries do not hold the heads", ldq);
     if (tokens == 0 || width == kv_rank) return 0;
     if (act_dtype == MRUN_F32)
-        latent_query_kernel<float><<<tokens, 256, 0, stream>>>((const float*)q, (const float2*)rot, rot_dims,
+        latent_query_kernel<float><<<tokens, 256, 0, stream>>>((const float*)q, ldq, (const float2*)rot, rot_dims,
                                                                interleaved, (float*)q_att, heads, dim, rot_dim,
                                                                kv_rank, width);
     else if (act_dtype == MRUN_BF16)
         latent_query_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
-            (const __nv_bfloat16*)q, (const float2*)rot, rot_dims, interleaved, (__nv_bfloat16*)q_att, heads, dim,
+            (const __nv_bfloat16*)q, ldq, (const float2*)rot, rot_dims, interleaved, (__nv_bfloat16*)q_att, heads, dim,
             rot_dim, kv_rank, width);
     else
         return mrun_set_error("latent_query: unknown dtype code %d", act_dtype);
@@ -412,22 +426,23 @@ MRUN_API int mrun_post_norm_add(float* stream_rows, const float* branch, const f
     return 0;
 }
 
-MRUN_API int mrun_route_top_k(const float* logits, float* weights, int* chosen, int tokens, int experts, int top,
-                              int kind, int renormalize, cudaStream_t stream) {
+MRUN_API int mrun_route_top_k(const float* logits, long ldz, const float* bias, float* weights, int* chosen, int tokens,
+                              int experts, int top, int kind, int renormalize, cudaStream_t stream) {
     MRUN_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts,
                  "route_top_k: bad sizes tokens=%d experts=%d top=%d", tokens, experts, top);
     MRUN_REQUIRE(experts <= 32 * ROUTE_MAX_PER_LANE, "route_top_k: %d experts exceed the supported %d", experts,
                  32 * ROUTE_MAX_PER_LANE);
-    MRUN_REQUIRE(kind == 0 || kind == 1, "route_top_k: unknown score function %d", kind);
+    MRUN_REQUIRE(kind >= 0 && kind <= 2, "route_top_k: unknown score function %d", kind);
+    MRUN_REQUIRE(ldz >= experts, "route_top_k: rows of %ld entries do not hold %d experts", ldz, experts);
     if (tokens == 0) return 0;
     const dim3 grid((tokens + 3) / 4);
     if (experts <= 32)
-        route_top_k_kernel<1><<<grid, 128, 0, stream>>>(logits, weights, chosen, tokens, experts, top, kind, renormalize);
+        route_top_k_kernel<1><<<grid, 128, 0, stream>>>(logits, ldz, bias, weights, chosen, tokens, experts, top, kind, renormalize);
     else if (experts <= 128)
-        route_top_k_kernel<4><<<grid, 128, 0, stream>>>(logits, weights, chosen, tokens, experts, top, kind, renormalize);
+        route_top_k_kernel<4><<<grid, 128, 0, stream>>>(logits, ldz, bias, weights, chosen, tokens, experts, top, kind, renormalize);
     else
-        route_top_k_kernel<ROUTE_MAX_PER_LANE><<<grid, 128, 0, stream>>>(logits, weights, chosen, tokens, experts, top,
-                                                                        kind, renormalize);
+        route_top_k_kernel<ROUTE_MAX_PER_LANE><<<grid, 128, 0, stream>>>(logits, ldz, bias, weights, chosen, tokens,
+                                                                        experts, top, kind, renormalize);
     MRUN_CHECK_LAUNCH("route_top_k");
     return 0;
 }

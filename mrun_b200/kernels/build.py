@@ -183,7 +183,7 @@ def build_host() -> str:
         return target
 
 
-CORE_SOURCES = ("common.cu", "elementwise.cu", "latent.cu", "routed.cu", "streams.cu", "recurrent.cu", "attention_diff.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tc5.cu",
+CORE_SOURCES = ("common.cu", "elementwise.cu", "layernorm.cu", "latent.cu", "routed.cu", "streams.cu", "recurrent.cu", "attention_diff.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tc5.cu",
                 "attention_generic.cu", "attention_latent.cu", "sampling.cu")
 
 

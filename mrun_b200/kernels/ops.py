@@ -74,6 +74,45 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     return out
 
 
+def add_layernorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                  out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """resid (+= delta) then out = (resid - mean) * rsqrt(variance + eps) * weight, the variance the
+    mean of the squared deviations; with ``rows`` only those rows are normed and resid is left as
+    it is.  ``delta`` is 32-bit or of ``out``'s dtype."""
+    _check(resid, "resid", torch.float32); _check(weight, "weight", torch.float32); _check(out, "out")
+    hidden = resid.shape[-1]
+    n_rows = resid.shape[0] if rows is None else rows.numel()
+    if delta is not None:
+        _check(delta, "delta")
+        if delta.shape != resid.shape or delta.dtype not in (torch.float32, out.dtype):
+            raise KernelError(f"add_layernorm: delta {tuple(delta.shape)} {delta.dtype} vs resid {tuple(resid.shape)}, "
+                              f"out {out.dtype}")
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    if weight.numel() != hidden or out.shape != (n_rows, hidden):
+        raise KernelError(f"add_layernorm: weight {tuple(weight.shape)}, out {tuple(out.shape)}, "
+                          f"expected hidden {hidden}, rows {n_rows}")
+    _lib.core().call("mrun_add_layernorm", _ptr(resid), _ptr(delta), dtype_code(delta.dtype if delta is not None else out.dtype),
+                     _ptr(weight), _c_float(eps), _ptr(out), dtype_code(out.dtype), _ptr(rows), _c_int(n_rows),
+                     _c_int(hidden), _stream())
+    return out
+
+
+def pair_norm_mean(a: torch.Tensor, b: torch.Tensor, weight_a: torch.Tensor, weight_b: torch.Tensor, eps: float,
+                   share: float = 0.5) -> torch.Tensor:
+    """float32 ``share * (rmsnorm(a) * weight_a + rmsnorm(b) * weight_b)`` row by row (eps inside the
+    root); ``a`` and ``b`` are float32 [rows, hidden]."""
+    for name, t in (("a", a), ("b", b), ("weight_a", weight_a), ("weight_b", weight_b)):
+        _check(t, name, torch.float32)
+    rows, hidden = a.shape
+    if b.shape != a.shape or weight_a.numel() != hidden or weight_b.numel() != hidden:
+        raise KernelError(f"pair_norm_mean: a {tuple(a.shape)}, b {tuple(b.shape)}, weights {weight_a.numel()} / {weight_b.numel()}")
+    out = torch.empty_like(a)
+    _lib.core().call("mrun_pair_norm_mean", _ptr(a), _ptr(b), _ptr(weight_a), _ptr(weight_b), _c_float(eps),
+                     _c_float(share), _ptr(out), _c_int(rows), _c_int(hidden), _stream())
+    return out
+
+
 def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor,
                  magnitude: float = 1.0) -> torch.Tensor:
     """out[t, j] = magnitude * (cos, sin)(positions[t] * inv_freq[j]); inv_freq is float64."""
@@ -158,6 +197,44 @@ def proj_norm_rope_cache(x: torch.Tensor, q_off: int, k_off: int, v_off: int, he
                      _c_int(rotary_dim if rot is not None else 0), _c_int(PAIRINGS[pairing]),
                      _ptr(slots if k_off >= 0 else None), _ptr(k_cache), _ptr(v_cache), _c_int(tokens), _c_int(heads),
                      _c_int(kv_heads), _c_int(dim), _c_int(vdim), _c_int(page_size), _stream())
+
+
+def head_norm_rope_cache(x: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, kv_heads: int, dim: int,
+                         vdim: int, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                         rot: Optional[torch.Tensor], rotary_dim: int, pairing: str, slots: Optional[torch.Tensor],
+                         k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], page_size: int) -> None:
+    """RMS norm of every q and k head over its own ``dim`` features (weights of ``dim`` entries that
+    the heads share; None: no norm), rotation of the first ``rotary_dim`` features of every head,
+    k and v into the pages ``slots`` names (key pages [pages, kv_heads, page, dim], value pages
+    [.., vdim]).  ``x``: rows whose q, k and v heads start at columns ``q_off``, ``k_off``,
+    ``v_off``; q is worked on in place.  ``v_off`` < 0: the values are the keys as projected,
+    before norm and rotation."""
+    ld = _strided_rows(x, "x")
+    tokens = x.shape[0]
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _check(w, name, torch.float32)
+            if w.numel() != dim:
+                raise KernelError(f"head_norm_rope_cache: {name} has {w.numel()} elements, a head has {dim}")
+    if rot is not None:
+        _check(rot, "rot", torch.float32)
+        if rot.shape != (tokens, rotary_dim // 2, 2):
+            raise KernelError(f"head_norm_rope_cache: rot is {tuple(rot.shape)}, expected {(tokens, rotary_dim // 2, 2)}")
+    if slots is not None:
+        _check(slots, "slots", torch.int32)
+        for name, c, n in (("k_cache", k_cache, dim), ("v_cache", v_cache, vdim)):
+            _check(c, name, x.dtype)
+            if c.dim() != 4 or c.shape[1:] != (kv_heads, page_size, n):
+                raise KernelError(f"head_norm_rope_cache: {name} is {tuple(c.shape)}, expected "
+                                  f"[pages, {kv_heads}, {page_size}, {n}]")
+    width = x.shape[1]
+    if q_off + heads * dim > width or k_off + kv_heads * dim > width or (v_off >= 0 and v_off + kv_heads * vdim > width):
+        raise KernelError("head_norm_rope_cache: the heads do not fit the rows")
+    _lib.core().call("mrun_head_norm_rope_cache", _ptr(x), _c_long(ld), _c_long(q_off), _c_long(k_off), _c_long(v_off),
+                     dtype_code(x.dtype), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(rot),
+                     _c_int(rotary_dim if rot is not None else 0), _c_int(PAIRINGS[pairing]), _ptr(slots), _ptr(k_cache),
+                     _ptr(v_cache), _c_int(tokens), _c_int(heads), _c_int(kv_heads), _c_int(dim), _c_int(vdim),
+                     _c_int(page_size), _stream())
 
 
 def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor,
@@ -698,9 +775,9 @@ def latent_prepare(down: torch.Tensor, q_weight: Optional[torch.Tensor], kv_weig
 
 def latent_query(q: torch.Tensor, rot: Optional[torch.Tensor], rot_dims: int, pairing: str, q_att: torch.Tensor,
                  heads: int, dim: int, rot_dim: int, kv_rank: int) -> None:
-    """``q`` [tokens, heads * (dim + rot_dim)]; fills ``q_att[t, h, kv_rank:]`` with the head's
-    rotated part and zeros ([tokens, heads, width])."""
-    _check(q, "q"); _check(q_att, "q_att", q.dtype)
+    """``q`` [tokens, heads * (dim + rot_dim)] (rows may be strided); fills ``q_att[t, h, kv_rank:]``
+    with the head's rotated part and zeros ([tokens, heads, width])."""
+    ldq = _strided_rows(q, "q"); _check(q_att, "q_att", q.dtype)
     tokens = q.shape[0]
     if q.shape != (tokens, heads * (dim + rot_dim)) or q_att.dim() != 3 or q_att.shape[:2] != (tokens, heads) \
             or q_att.shape[2] < kv_rank + rot_dim:
@@ -709,7 +786,7 @@ def latent_query(q: torch.Tensor, rot: Optional[torch.Tensor], rot_dims: int, pa
         _check(rot, "rot", torch.float32)
         if rot.shape != (tokens, rot_dims // 2, 2):
             raise KernelError(f"latent_query: rot is {tuple(rot.shape)}, expected {(tokens, rot_dims // 2, 2)}")
-    _lib.core().call("mrun_latent_query", _ptr(q), dtype_code(q.dtype), _ptr(rot), _c_int(rot_dims),
+    _lib.core().call("mrun_latent_query", _ptr(q), _c_long(ldq), dtype_code(q.dtype), _ptr(rot), _c_int(rot_dims),
                      _c_int(PAIRINGS[pairing]), _ptr(q_att), _c_int(tokens), _c_int(heads), _c_int(dim),
                      _c_int(rot_dim), _c_int(kv_rank), _c_int(q_att.shape[2]), _stream())
 
@@ -740,22 +817,32 @@ def post_norm_add(stream: torch.Tensor, branch: torch.Tensor, w_post: torch.Tens
     return out
 
 
-ROUTER_SCORES = {"softmax": 0, "sigmoid": 1}
+ROUTER_SCORES = {"softmax": 0, "sigmoid": 1, "logit": 2}
 
 
 def route_top_k(logits: torch.Tensor, top: int, score: str = "softmax", renormalize: bool = False,
-                chosen: Optional[torch.Tensor] = None) -> torch.Tensor:
+                chosen: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """float32 [tokens, experts]: each token's ``top`` largest scores at their experts' places
-    (divided by their sum if ``renormalize``), zero elsewhere."""
-    _check(logits, "logits", torch.float32)
+    (divided by their sum if ``renormalize``), zero elsewhere.  ``score`` = ``"logit"``: the logits
+    themselves are ranked and the chosen experts weigh the softmax over the chosen logits only.
+    ``bias`` (float32, one entry an expert) is added to the logits first.  ``logits`` may be the
+    first columns of wider rows (a product padded to a vendor-friendly width)."""
+    _check(logits, "logits", torch.float32, dense=False)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError(f"route_top_k: logits has strides {logits.stride()}, expected rows of unit stride")
     tokens, experts = logits.shape
-    weights = torch.empty_like(logits)
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.numel() != experts:
+            raise KernelError(f"route_top_k: bias has {bias.numel()} entries for {experts} experts")
+    weights = torch.empty((tokens, experts), dtype=torch.float32, device=logits.device)
     if chosen is not None:
         _check(chosen, "chosen", torch.int32)
         if chosen.shape != (tokens, top):
             raise KernelError(f"route_top_k: chosen is {tuple(chosen.shape)}, expected {(tokens, top)}")
-    _lib.core().call("mrun_route_top_k", _ptr(logits), _ptr(weights), _ptr(chosen), _c_int(tokens), _c_int(experts),
-                     _c_int(top), _c_int(ROUTER_SCORES[score]), _c_int(1 if renormalize else 0), _stream())
+    _lib.core().call("mrun_route_top_k", _ptr(logits), _c_long(logits.stride(0)), _ptr(bias), _ptr(weights), _ptr(chosen),
+                     _c_int(tokens), _c_int(experts), _c_int(top), _c_int(ROUTER_SCORES[score]),
+                     _c_int(1 if renormalize else 0), _stream())
     return weights
 
 

@@ -28,6 +28,9 @@ def norm_add(norm, resid: torch.Tensor, delta):
     takes it as it is."""
     if isinstance(delta, ops.PENDING) and not getattr(norm, "accepts_pending", False):
         delta = delta.compute()
+    if isinstance(delta, torch.Tensor) and delta.dtype == torch.float32 and resid.dtype == torch.float32 \
+            and getattr(norm, "act", torch.float32) != torch.float32 and not getattr(norm, "accepts_wide_delta", False):
+        delta = delta.to(norm.act)      # a 32-bit branch output in front of a norm that takes the activation type
     return norm.add_forward(resid, delta)
 
 
@@ -43,17 +46,21 @@ class PreNormBlock:
     @staticmethod
     def tensor_specs(spec: LayerSpec, prefix: str = "") -> list[TensorSpec]:
         p = spec.prefix
-        return (NORMS.tensor_specs(spec.mixer_norm, f"{p}.{spec.mixer_norm_prefix}")
-                + MIXERS.tensor_specs(spec.mixer, f"{p}.{spec.mixer_prefix}")
-                + NORMS.tensor_specs(spec.feed_forward_norm, f"{p}.{spec.feed_forward_norm_prefix}")
-                + FEED_FORWARDS.tensor_specs(spec.feed_forward, f"{p}.{spec.feed_forward_prefix}"))
+        out = (NORMS.tensor_specs(spec.mixer_norm, f"{p}.{spec.mixer_norm_prefix}")
+               + MIXERS.tensor_specs(spec.mixer, f"{p}.{spec.mixer_prefix}"))
+        if spec.feed_forward is not None:       # a layer may be a mixer only
+            out += (NORMS.tensor_specs(spec.feed_forward_norm, f"{p}.{spec.feed_forward_norm_prefix}")
+                    + FEED_FORWARDS.tensor_specs(spec.feed_forward, f"{p}.{spec.feed_forward_prefix}"))
+        return out
 
     def __init__(self, spec: LayerSpec, tensors, runtime: Runtime):
         mine = local(tensors, spec.prefix)
         self.mixer_norm = NORMS.build(spec.mixer_norm, local(mine, spec.mixer_norm_prefix), runtime)
         self.mixer = MIXERS.build(spec.mixer, local(mine, spec.mixer_prefix), runtime)
-        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, local(mine, spec.feed_forward_norm_prefix), runtime)
-        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, local(mine, spec.feed_forward_prefix), runtime)
+        self.feed_forward_norm = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, local(mine, spec.feed_forward_norm_prefix), runtime)
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, local(mine, spec.feed_forward_prefix), runtime)
         self._mixer_defers = bool(getattr(self.mixer, "can_defer_output", False))
         self._feed_forward_defers = bool(getattr(self.feed_forward, "can_defer_output", False))
 
@@ -65,6 +72,8 @@ class PreNormBlock:
             a = self.mixer.forward(h, ctx, cache, defer_output=True)
         else:
             a = self.mixer.forward(h, ctx, cache)
+        if self.feed_forward is None:
+            return a
         h = part_input(self.feed_forward, norm_add(self.feed_forward_norm, resid, a))
         if self._feed_forward_defers:
             return self.feed_forward.forward(h, ctx, defer_output=True)

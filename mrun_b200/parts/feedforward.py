@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.spec import GatedMLPSpec, TensorSpec
+from ..config.spec import ClampedGatedMLPSpec, GatedMLPSpec, TensorSpec
 from ..kernels import ops
 from .base import Runtime, register_feed_forward
 
@@ -75,6 +75,47 @@ class GatedMLP:
             gate_up = ops.linear(x, self.w_gate_up, bias=self.b_gate_up)
             act = torch.empty((gate_up.shape[0], self.spec.intermediate), dtype=gate_up.dtype, device=gate_up.device)
             ops.swiglu(gate_up, act, interleaved=self.interleaved, activation=name)
+        if defer_output:
+            return ops.linear_or_pending(act, self.w_down, self.b_down)
+        return ops.linear(act, self.w_down, bias=self.b_down)
+
+
+@register_feed_forward("clamped_gated_mlp")
+class ClampedGatedMLP:
+    """Dense gated feed-forward with clamped branches (the formulas are with
+    :class:`ClampedGatedMLPSpec`): one product makes [gate | up] with their biases,
+    ``ops.clamped_glu`` applies min / clamp, the gate's sigmoid and the +1, one product goes down
+    with its bias.  The checkpoint names the matrices ``gate``, ``up``, ``down`` and their biases
+    ``gate.b``, ``up.b``, ``down.b``."""
+
+    can_defer_output = True
+
+    @staticmethod
+    def tensor_specs(spec: ClampedGatedMLPSpec, prefix: str):
+        out = [TensorSpec(f"{prefix}.gate", (spec.intermediate, spec.hidden)),
+               TensorSpec(f"{prefix}.up", (spec.intermediate, spec.hidden)),
+               TensorSpec(f"{prefix}.down", (spec.hidden, spec.intermediate))]
+        if spec.biases:
+            out += [TensorSpec(f"{prefix}.gate.b", (spec.intermediate,)), TensorSpec(f"{prefix}.up.b", (spec.intermediate,)),
+                    TensorSpec(f"{prefix}.down.b", (spec.hidden,))]
+        return out
+
+    def __init__(self, spec: ClampedGatedMLPSpec, tensors, runtime: Runtime):
+        self.spec = spec
+        self.w_gate_up = runtime.matrix(torch.cat([tensors["gate"], tensors["up"]], dim=0))
+        self.w_down = runtime.matrix(tensors["down"])
+        self.b_gate_up = self.b_down = None
+        if spec.biases:
+            self.b_gate_up = runtime.vector_f32(torch.cat([tensors["gate.b"].to(torch.float32), tensors["up.b"].to(torch.float32)]))
+            self.b_down = runtime.vector_f32(tensors["down.b"])
+
+    def activation_elements(self) -> int:
+        return 3 * self.spec.intermediate
+
+    def forward(self, x, ctx, defer_output: bool = False):
+        s = self.spec
+        u = ops.linear(x, self.w_gate_up, bias=self.b_gate_up)
+        act = ops.clamped_glu(u, None, 1, s.intermediate, s.limit, s.alpha)
         if defer_output:
             return ops.linear_or_pending(act, self.w_down, self.b_down)
         return ops.linear(act, self.w_down, bias=self.b_down)

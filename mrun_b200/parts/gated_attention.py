@@ -1,11 +1,14 @@
-"""Grouped-query attention with keys and values of different sizes, a norm of q and k over the
-whole projection, a sink term in the softmax and an output gate per head (the formulas are with
-:class:`GatedAttentionSpec`).
+"""Grouped-query attention with keys and values of different sizes, a norm of q and k (over the
+whole projection, or head by head), a sink term in the softmax, an output gate per head, values
+that may be the unnormed keys, and a causal, sliding-window or chunked mask (the formulas are
+with :class:`GatedAttentionSpec`).
 
-One product makes [q | k | v | gate] (or [q | gate] for a layer that reads another layer's pages);
-``ops.proj_norm_rope_cache`` norms q and k, rotates them and writes k and v into the pages; the
+One product makes [q | k | v | gate] (or [q | gate] for a layer that reads another layer's pages,
+[q | k] for one whose values are its keys); ``ops.proj_norm_rope_cache`` or
+``ops.head_norm_rope_cache`` norms q and k, rotates them and writes k and v into the pages; the
 attention kernel applies the sink and the gate's sigmoid to every head's output; the output
-projection follows.  Scores, softmax, the sink and the gate are 32-bit in both precisions.
+projection follows.  Scores, softmax, the sink and the gate are 32-bit in both precisions.  A
+chunked mask reaches the attention kernels as a negative window (minus the chunk's size).
 
 Kernels: bfloat16 with keys and values of one size that the tensor-core attention takes go
 through the framework's paged kernels (tcgen05 prompt tiles, TMA decode; the sink enters their
@@ -40,11 +43,14 @@ class GatedAttention:
         out = [TensorSpec(f"{prefix}.q", (nq, spec.hidden)),
                TensorSpec(f"{prefix}.o", (spec.hidden, spec.heads * spec.vdim))]
         if spec.own_kv:
-            out += [TensorSpec(f"{prefix}.k", (nk, spec.hidden)), TensorSpec(f"{prefix}.v", (nv, spec.hidden))]
+            out.append(TensorSpec(f"{prefix}.k", (nk, spec.hidden)))
+            if spec.values != "keys":
+                out.append(TensorSpec(f"{prefix}.v", (nv, spec.hidden)))
         if spec.qk_norm is not None:
-            out.append(TensorSpec(f"{prefix}.q.norm", (nq,), "norm"))
+            per_head = spec.qk_norm == "head"
+            out.append(TensorSpec(f"{prefix}.q.norm", (spec.dim if per_head else nq,), "norm"))
             if spec.own_kv:
-                out.append(TensorSpec(f"{prefix}.k.norm", (nk,), "norm"))
+                out.append(TensorSpec(f"{prefix}.k.norm", (spec.dim if per_head else nk,), "norm"))
         if spec.head_gate:
             out.append(TensorSpec(f"{prefix}.g", (spec.heads, spec.hidden)))
         return out
@@ -52,13 +58,27 @@ class GatedAttention:
     def __init__(self, spec: GatedAttentionSpec, tensors, runtime: Runtime):
         if spec.heads % spec.kv_heads:
             raise ValueError(f"heads={spec.heads} is not a multiple of kv_heads={spec.kv_heads}")
-        if spec.qk_norm not in (None, "projection"):
-            raise ValueError(f"the q/k norm of this attention works over the whole projection, not {spec.qk_norm!r}")
+        if spec.qk_norm not in (None, "projection", "head"):
+            raise ValueError(f"the q/k norm of this attention works over the whole projection or head by head, "
+                             f"not {spec.qk_norm!r}")
+        if spec.values not in ("projection", "keys"):
+            raise ValueError(f"values come from a projection of their own or are the keys, not {spec.values!r}")
+        self.keys_as_values = spec.values == "keys"
+        if self.keys_as_values and (spec.vdim != spec.dim or not spec.own_kv):
+            raise ValueError("values that are the keys have the keys' size and belong to a layer with keys of its own")
+        if spec.window is not None and spec.chunk is not None:
+            raise ValueError("an attention has a sliding window or a chunked mask, not both")
+        if (spec.window is not None and spec.window < 1) or (spec.chunk is not None and spec.chunk < 1):
+            raise ValueError("a window or a chunk holds at least one position")
         self.spec = spec
         self.runtime = runtime
+        # what the attention kernels take as their window: W, 0 for none, -C for chunks of C
+        self.mask = -spec.chunk if spec.chunk is not None else (spec.window or 0)
         self.nq, self.nk, self.nv = spec.heads * spec.dim, spec.kv_heads * spec.dim, spec.kv_heads * spec.vdim
-        parts = [tensors["q"]] + ([tensors["k"], tensors["v"]] if spec.own_kv else [])
-        self.k_off, self.v_off = (self.nq, self.nq + self.nk) if spec.own_kv else (-1, -1)
+        parts = [tensors["q"]] + ([tensors["k"]] + ([] if self.keys_as_values else [tensors["v"]]) if spec.own_kv else [])
+        self.k_off, self.v_off = (self.nq, -1 if self.keys_as_values else self.nq + self.nk) if spec.own_kv else (-1, -1)
+        # the kernel that norms head by head also serves the layers that norm nothing special
+        self.per_head = spec.qk_norm == "head" or self.keys_as_values
         self.gate_off = sum(p.shape[0] for p in parts)
         if spec.head_gate:
             parts.append(tensors["g"])
@@ -83,7 +103,9 @@ class GatedAttention:
         s = self.spec
         if not s.own_kv:
             return None
-        return PagedKV(s.kv_heads, s.dim, s.window, value_dim=s.vdim if s.vdim != s.dim else None)
+        # a chunk's keys lie within the last `chunk` positions: the pages before them are given back
+        return PagedKV(s.kv_heads, s.dim, s.chunk if s.chunk is not None else s.window,
+                       value_dim=s.vdim if s.vdim != s.dim else None)
 
     def activation_elements(self) -> int:
         s = self.spec
@@ -100,18 +122,23 @@ class GatedAttention:
         y = ops.linear(x, self.w_in)
         rot = self.position.rotation(ctx) if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
-        ops.proj_norm_rope_cache(y, 0, self.k_off, self.v_off, s.heads, s.kv_heads, s.dim, s.vdim, self.q_weight,
-                                 self.k_weight, s.eps, rot, rotary_dim, self.pairing,
-                                 group.slot_mapping if s.own_kv else None, cache.k, cache.v, self.runtime.page_size)
+        if self.per_head:
+            ops.head_norm_rope_cache(y, 0, max(self.k_off, 0), self.v_off, s.heads, s.kv_heads, s.dim, s.vdim,
+                                     self.q_weight, self.k_weight, s.eps, rot, rotary_dim, self.pairing,
+                                     group.slot_mapping if s.own_kv else None, cache.k, cache.v, self.runtime.page_size)
+        else:
+            ops.proj_norm_rope_cache(y, 0, self.k_off, self.v_off, s.heads, s.kv_heads, s.dim, s.vdim, self.q_weight,
+                                     self.k_weight, s.eps, rot, rotary_dim, self.pairing,
+                                     group.slot_mapping if s.own_kv else None, cache.k, cache.v, self.runtime.page_size)
         gate = y[:, self.gate_off:self.gate_off + s.heads] if s.head_gate else None
         out = torch.empty((x.shape[0], s.heads * s.vdim), dtype=x.dtype, device=x.device)
         if self.tensor_cores:
-            paged_attention(y, y.stride(0), out, cache, group, ctx, s.heads, s.softmax_scale, s.window or 0, sink=s.sink)
+            paged_attention(y, y.stride(0), out, cache, group, ctx, s.heads, s.softmax_scale, self.mask, sink=s.sink)
             if gate is not None:
                 ops.head_gate(out, gate, s.heads)
         else:
             ops.paged_attention_generic(y, y.stride(0), out, cache.k, cache.v, group.block_tables, ctx.token_slot,
-                                        ctx.positions, s.heads, s.softmax_scale, s.window or 0, sink=s.sink, gate=gate)
+                                        ctx.positions, s.heads, s.softmax_scale, self.mask, sink=s.sink, gate=gate)
         if defer_output:
             return ops.linear_or_pending(out, self.w_o)
         return ops.linear(out, self.w_o)

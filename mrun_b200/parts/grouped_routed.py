@@ -24,6 +24,7 @@ from ..kernels import ops
 from . import routed
 from .base import Runtime, register_feed_forward
 
+SCORES = ("sigmoid", "logit")
 ACTIVATIONS = {"silu": 1.0}       # the gate's function as the factor inside its sigmoid: g * sigmoid(factor * g)
 
 
@@ -34,6 +35,8 @@ class GroupedRoutedMLP:
     @staticmethod
     def tensor_specs(spec: GroupedRoutedMLPSpec, prefix: str):
         out = [TensorSpec(f"{prefix}.router", (spec.experts, spec.hidden))]
+        if spec.router_bias:
+            out.append(TensorSpec(f"{prefix}.router.b", (spec.experts,)))
         sizes = [(f"e{e}", spec.expert_ff) for e in range(spec.experts)] + ([("shared", spec.shared_ff)] if spec.shared_ff else [])
         for name, ff in sizes:
             out += [TensorSpec(f"{prefix}.{name}.gate", (ff, spec.hidden)),
@@ -50,7 +53,12 @@ class GroupedRoutedMLP:
                 or not 1 <= spec.top <= spec.keep_groups * (spec.experts // spec.groups):
             raise ValueError(f"{spec.experts} experts in {spec.groups} groups of which {spec.keep_groups} stay "
                              f"cannot give {spec.top} choices")
+        if spec.score not in SCORES:
+            raise ValueError(f"no kernel has the router score {spec.score!r} (known: {', '.join(SCORES)})")
+        if spec.score == "logit" and (spec.groups != 1 or (spec.shared_ff and spec.shared_gate)):
+            raise ValueError("a router that ranks its logits has no groups and no gated shared expert")
         self.spec = spec
+        self.router_bias = runtime.vector_f32(tensors["router.b"]) if spec.router_bias else None
         self.alpha = ACTIVATIONS[spec.activation]
         names = [f"e{e}" for e in range(spec.experts)] + (["shared"] if spec.shared_ff else [])
         self.gated_shared = bool(spec.shared_ff and spec.shared_gate)
@@ -80,6 +88,10 @@ class GroupedRoutedMLP:
     def _route(self, x, chosen=None):
         s = self.spec
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)[:, :self.router_rows]
+        if s.score == "logit":      # the softmax over the chosen logits only
+            return ops.route_top_k(logits, s.top, "logit", chosen=chosen, bias=self.router_bias), None
+        if self.router_bias is not None:
+            logits = ops.add_bias(logits.contiguous(), self.router_bias)
         return ops.route_grouped(logits, s.experts, s.top, s.groups, s.keep_groups, s.group_top, s.route_scale, chosen=chosen)
 
     def _sorted_forward(self, x):

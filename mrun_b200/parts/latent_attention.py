@@ -15,6 +15,10 @@ prefill, decode and mixed steps take the paths they take for grouped-query atten
 than those kernels' 256 features (a latent of 512, say) go to a tensor-core kernel of their own
 (``csrc/attention_latent.cu``: a block a token and 16 heads, a quarter of the value columns a warp).
 
+A layer without a query latent (``q_rank`` = 0) has one query projection ``q`` straight from the
+input; it rides in the same product as the key/value down-projection.  ``window`` reaches the
+attention kernels as it does for grouped-query attention.
+
 Per step: one product for both down-projections (their weights stacked), one kernel that norms
 the two latents, rotates r and writes the cache row, the query up-projection, a per-head product
 with U_h^T, one kernel that rotates the queries' rotated parts into the query rows, attention, a
@@ -38,10 +42,13 @@ class LatentAttention:
     @staticmethod
     def tensor_specs(spec: LatentAttentionSpec, prefix: str):
         s = spec
-        return [
-            TensorSpec(f"{prefix}.dq", (s.q_rank, s.hidden)),
-            TensorSpec(f"{prefix}.dq.norm", (s.q_rank,), "norm"),
-            TensorSpec(f"{prefix}.uq", (s.heads * (s.dim + s.rot_dim), s.q_rank)),
+        if s.q_rank:
+            query = [TensorSpec(f"{prefix}.dq", (s.q_rank, s.hidden)),
+                     TensorSpec(f"{prefix}.dq.norm", (s.q_rank,), "norm"),
+                     TensorSpec(f"{prefix}.uq", (s.heads * (s.dim + s.rot_dim), s.q_rank))]
+        else:
+            query = [TensorSpec(f"{prefix}.q", (s.heads * (s.dim + s.rot_dim), s.hidden))]
+        return query + [
             TensorSpec(f"{prefix}.dkv", (s.kv_rank + s.rot_dim, s.hidden)),
             TensorSpec(f"{prefix}.dkv.norm", (s.kv_rank,), "norm"),
             TensorSpec(f"{prefix}.uk", (s.heads * s.dim, s.kv_rank)),
@@ -52,10 +59,14 @@ class LatentAttention:
     def __init__(self, spec: LatentAttentionSpec, tensors, runtime: Runtime):
         s = self.spec = spec
         self.runtime = runtime
-        self.w_down = runtime.matrix(torch.cat([tensors["dq"], tensors["dkv"]], dim=0))
-        self.q_norm = runtime.vector_f32(tensors["dq.norm"])
+        if s.window is not None and s.window < 1:
+            raise ValueError("a window holds at least one position")
+        # the first product: [query latent | key/value latent | shared key part], or, without a
+        # query latent, [queries | key/value latent | shared key part]
+        self.w_down = runtime.matrix(torch.cat([tensors["dq" if s.q_rank else "q"], tensors["dkv"]], dim=0))
+        self.q_norm = runtime.vector_f32(tensors["dq.norm"]) if s.q_rank else None
         self.kv_norm = runtime.vector_f32(tensors["dkv.norm"])
-        self.w_uq = runtime.matrix(tensors["uq"])
+        self.w_uq = runtime.matrix(tensors["uq"]) if s.q_rank else None
         # U_h^T per head, [heads, kv_rank, dim]: the per-head product takes weights as [out, in]
         self.w_uk_t = runtime.matrix(tensors["uk"].view(s.heads, s.dim, s.kv_rank).transpose(1, 2))
         self.w_uv = runtime.matrix(tensors["uv"].view(s.heads, s.vdim, s.kv_rank))
@@ -71,7 +82,7 @@ class LatentAttention:
         self.graph_safe = not (supports_tensor_cores(runtime.precision.act, self.width, s.heads) and s.heads > 16)
 
     def cache_need(self):
-        return PagedLatent(self.width)
+        return PagedLatent(self.width, self.spec.window)
 
     def activation_elements(self) -> int:
         s = self.spec
@@ -83,17 +94,24 @@ class LatentAttention:
         group = ctx.group(cache.group_key)
         down = ops.linear(x, self.w_down)
         rot = self.position.rotation(ctx) if self.position is not None else None
-        cq = torch.empty((tokens, s.q_rank), dtype=x.dtype, device=x.device)
-        ops.latent_prepare(down, self.q_norm, self.kv_norm, s.eps, rot, self.rot_dims, self.pairing,
-                           group.slot_mapping if cache.writable else None, cq, cache.k, s.q_rank, s.kv_rank, s.rot_dim)
-        q = ops.linear(cq, self.w_uq)
+        slots = group.slot_mapping if cache.writable else None
+        if s.q_rank:
+            cq = torch.empty((tokens, s.q_rank), dtype=x.dtype, device=x.device)
+            ops.latent_prepare(down, self.q_norm, self.kv_norm, s.eps, rot, self.rot_dims, self.pairing, slots, cq,
+                               cache.k, s.q_rank, s.kv_rank, s.rot_dim)
+            q = ops.linear(cq, self.w_uq)
+        else:
+            nq = s.heads * (s.dim + s.rot_dim)
+            q = down[:, :nq]
+            ops.latent_prepare(down[:, nq:], None, self.kv_norm, s.eps, rot, self.rot_dims, self.pairing, slots, None,
+                               cache.k, 0, s.kv_rank, s.rot_dim)
         q_att = torch.empty((tokens, s.heads, width), dtype=x.dtype, device=x.device)
-        ops.linear_per_head(q.view(tokens, s.heads, s.dim + s.rot_dim)[:, :, :s.dim], self.w_uk_t,
+        ops.linear_per_head(q.unflatten(1, (s.heads, s.dim + s.rot_dim))[:, :, :s.dim], self.w_uk_t,
                             q_att[:, :, :s.kv_rank])
         ops.latent_query(q, rot, self.rot_dims, self.pairing, q_att, s.heads, s.dim, s.rot_dim, s.kv_rank)
         mixed = torch.empty((tokens, s.heads * width), dtype=x.dtype, device=x.device)
         paged_attention(q_att.view(tokens, s.heads * width), s.heads * width, mixed, cache, group, ctx, s.heads,
-                        s.softmax_scale, 0, value_dim=s.kv_rank)
+                        s.softmax_scale, s.window or 0, value_dim=s.kv_rank)
         value = torch.empty((tokens, s.heads, s.vdim), dtype=x.dtype, device=x.device)
         ops.linear_per_head(mixed.view(tokens, s.heads, width)[:, :, :s.kv_rank], self.w_uv, value)
         value = value.view(tokens, s.heads * s.vdim)

@@ -7,7 +7,7 @@ from typing import Optional
 
 import torch
 
-from ..config.spec import RMSNormSpec, TensorSpec
+from ..config.spec import LayerNormSpec, RMSNormSpec, TensorSpec
 from ..kernels import ops
 from .base import Runtime, register_norm
 
@@ -63,6 +63,50 @@ class RMSNorm:
             delta = delta.compute()
         out = torch.empty((rows.numel(), self.size), dtype=self.act, device=resid.device)
         return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.add_forward(x.to(torch.float32), None)
+
+
+@register_norm("layernorm")
+class LayerNorm:
+    """Layer norm with a weight and no bias, in 32-bit: ``y = (x - mean) * rsqrt(var + eps) * w``,
+    the variance taken from the deviations.  The residual sum rides in the same kernel; a branch
+    output may come in 32-bit or in the activation type."""
+
+    @staticmethod
+    def tensor_specs(spec: LayerNormSpec, prefix: str):
+        return [TensorSpec(prefix if spec.bare else f"{prefix}.weight", (spec.size,), "norm")]
+
+    # ``delta`` may be a product that has not run yet: above 16 bfloat16 rows the vendor GEMM adds
+    # it into the 32-bit stream itself, otherwise it is computed first
+    accepts_pending = True
+    accepts_wide_delta = True       # ``delta`` may be 32-bit where the activations are not
+
+    def __init__(self, spec: LayerNormSpec, tensors, runtime: Runtime):
+        self.size, self.eps = spec.size, float(spec.eps)
+        self.weight = runtime.vector_f32(tensors["" if spec.bare else "weight"])
+        self.act = runtime.precision.act
+
+    def _settle(self, resid: torch.Tensor, delta, in_place: bool):
+        if isinstance(delta, ops.PendingLinear):
+            if in_place and ops.accumulate_ok(delta, resid):
+                ops.linear_add_into(resid, delta)
+                return None
+            return delta.compute()
+        if isinstance(delta, ops.PENDING):
+            return delta.compute()
+        return delta
+
+    def add_forward(self, resid: torch.Tensor, delta):
+        delta = self._settle(resid, delta, True)
+        out = torch.empty(resid.shape, dtype=self.act, device=resid.device)
+        return ops.add_layernorm(resid, delta, self.weight, self.eps, out)
+
+    def rows_forward(self, resid: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        delta = self._settle(resid, delta, False)
+        out = torch.empty((rows.numel(), self.size), dtype=self.act, device=resid.device)
+        return ops.add_layernorm(resid, delta, self.weight, self.eps, out, rows=rows)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.add_forward(x.to(torch.float32), None)

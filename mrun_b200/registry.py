@@ -67,10 +67,12 @@ def _register_builtin() -> None:
     from .config.zasesun import ZasesunConfig
     from .config.balivik import BalivikConfig
     from .config.fikudra import FikudraConfig
+    from .config.nisotar import NisotarConfig
     register_architecture(Qwen3Config)
     register_architecture(ZasesunConfig)
     register_architecture(BalivikConfig)
     register_architecture(FikudraConfig)
+    register_architecture(NisotarConfig)
 
 
 _register_builtin()
