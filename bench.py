@@ -3,7 +3,7 @@
 random weights and seeded synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
-                    [--shape 8b|4b|32b] [--serve] [--design zasesun|balivik|fikudra]
+                    [--shape 8b|4b|32b] [--serve] [--design zasesun|balivik|fikudra|nisotar]
 
 A *step* is one decode step of a batch of 8 requests that each hold 1,024 tokens of context.
 ``value`` is decoded tokens per second over exactly K steps, timed on the device with CUDA events
@@ -22,6 +22,10 @@ and a channel-wise delta rule under four residual streams, dense and table-route
 a gate per head that may read an earlier layer's pages, group-limited routed experts with a shared
 expert, four residual streams, a hashed bigram embedding) beside the Balivik decoder at equal
 widths, depths, head counts and expert sizes.
+``--design nisotar`` measures the Nisotar decoder (a chunked attention whose values are its keys
+beside a gated delta rule, attention and latent attention under sliding windows, all under layer
+norms; a clamped dense and logit-routed feed-forwards) beside the Fikudra decoder at equal widths,
+depths, head counts and expert sizes.
 """
 from __future__ import annotations
 
@@ -406,28 +410,115 @@ def fikudra_counts(cfg: dict, tokens: int):
     return flops + 2.0 * cfg["vocab"] * h, row_bytes, state_bytes
 
 
+# Layer sizes for --design nisotar: (Nisotar sizes, the Fikudra sizes of equal width, depth, head
+# counts and expert sizes, from the table above).  Eight layers: parallel (a chunked attention whose
+# values are its keys beside a gated delta rule), attention under a sliding window, latent attention
+# under a sliding window, and again; keys and values of one size (the tensor-core attention
+# kernels), half of the features rotated, the latent row 256 features wide; the first layer's
+# feed-forward dense with clamped branches, the others mixtures of 8 experts of which 2 are chosen.
+def _nisotar_sizes(width, heads, kv_heads, att_dim, dim, experts, top, expert_ff, dense_ff, rank, layers, vocab):
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": att_dim, "vdim": att_dim, "scale": att_dim ** -0.5,
+           "mask": {"size": 512},
+           "rot": {"base": 10000.0, "dims": att_dim // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": att_dim, "vdim": att_dim, "scale": att_dim ** -0.5,
+            "mask": {"size": 256}, "rot": {"base": 100000.0, "dims": att_dim // 2}}
+    right = {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4, "decay_rank": rank, "gate_rank": rank}
+    lat = {"heads": heads, "dim": att_dim, "rot_dim": att_dim // 2, "vdim": att_dim, "kv_rank": 256 - att_dim // 2,
+           "scale": (att_dim + att_dim // 2) ** -0.5, "mask": {"size": 384}, "rot": {"base": 10000.0, "dims": att_dim // 2}}
+    kinds = [("parallel", {"left": left, "right": right}), ("attention", att), ("latent_attention", lat)]
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}}
+    dense = {"kind": "dense", "ff": dense_ff, "limit": 7.0}
+    return {"architecture": "Nisotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.5},
+            "layers": [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": moe if i else dense} for i in range(layers)]}
+
+
+NISOTAR_SIZES = {
+    "w2048": (_nisotar_sizes(2048, 16, 4, 128, 128, 8, 2, 2048, 8192, 128, 8, 32768), FIKUDRA_SIZES["w2048"][0]),
+    "w4096": (_nisotar_sizes(4096, 32, 8, 128, 128, 8, 2, 3072, 12288, 256, 8, 32768), FIKUDRA_SIZES["w4096"][0]),
+}
+
+
+def nisotar_counts(cfg: dict, tokens: int, context: int):
+    """(FLOPs of a prompt of ``tokens`` tokens as the design states them, bytes of cache rows a
+    decoded token at ``context`` reads over all layers divided by ``context``, bytes of one
+    request's recurrent states over all layers) of a Nisotar configuration: products count two
+    FLOPs a weight and token (a routed layer its chosen experts), an attention the scores and
+    weighted sums of every key its mask lets it see, the delta rule the decay, the correction, the
+    update and the read-out of its state for every token."""
+    h, flops, row_bytes, state_bytes = cfg["width"], 0.0, 0.0, 0
+
+    def seen(size, chunked):        # (token, key) pairs of the prompt that the mask lets through
+        if chunked:
+            whole, rest = divmod(tokens, size)
+            return whole * size * (size + 1) / 2.0 + rest * (rest + 1) / 2.0
+        short = min(tokens, size)
+        return short * (short + 1) / 2.0 + max(0, tokens - size) * size
+
+    def softmax_attention(m, chunked, keys):
+        nonlocal flops, row_bytes
+        groups = m.get("kv_heads") or m["heads"]
+        flops += 2.0 * seen(m["mask"]["size"], chunked) * m["heads"] * (m["dim"] + m["vdim"])
+        held = min(context, m["mask"]["size"]) if not chunked else (m["mask"]["size"] + 1) / 2.0
+        row_bytes += 2 * groups * (m["dim"] + m["vdim"]) * held / context
+        return h * (m["heads"] * (m["dim"] + m["vdim"]) + groups * (m["dim"] + (0 if keys else m["vdim"])))
+    for layer in cfg["layers"]:
+        m, kind = layer["mixer"], layer["type"]
+        if kind == "attention":
+            params = softmax_attention(m, False, False)
+        elif kind == "latent_attention":
+            params = h * (m["heads"] * (m["dim"] + m["rot_dim"] + m["vdim"]) + m["kv_rank"] + m["rot_dim"]) \
+                + m["kv_rank"] * m["heads"] * (m["dim"] + m["vdim"])
+            flops += 2.0 * seen(m["mask"]["size"], False) * m["heads"] * (m["dim"] + m["rot_dim"] + m["vdim"])
+            row_bytes += 2 * (m["kv_rank"] + m["rot_dim"]) * min(context, m["mask"]["size"]) / context
+        else:
+            params = softmax_attention(m["left"], True, True)
+            r = m["right"]
+            inner, keyed = r["heads"] * r["vdim"], r["heads"] * r["dim"]
+            params += h * (2 * r["kv_heads"] * r["dim"] + 2 * inner + r["heads"] + r["decay_rank"] + r["gate_rank"]) \
+                + keyed * r["decay_rank"] + inner * r["gate_rank"]
+            flops += 2.0 * tokens * r["heads"] * 4 * r["dim"] * r["vdim"]
+            state_bytes += 4 * r["heads"] * r["dim"] * r["vdim"]
+        mlp = layer["mlp"]
+        if mlp and mlp["kind"] == "dense":
+            params += 3 * h * mlp["ff"]
+        elif mlp:
+            params += h * mlp["router"]["experts"] + 3 * h * mlp["router"]["top"] * mlp["expert"]["ff"]
+        flops += 2.0 * tokens * params
+    return flops + 2.0 * cfg["vocab"] * h, row_bytes, state_bytes
+
+
 def compare_designs(args, peaks: dict) -> int:
     """Prefill of 2,048 tokens and decode at batch 8 with 1,024-token contexts, the named design
-    beside Qwen3 (Fikudra: beside Balivik) at equal sizes, each through the same ``Executor.step``
-    and captured decode step."""
+    beside Qwen3 (Fikudra: beside Balivik; Nisotar: beside Fikudra) at equal sizes, each through
+    the same ``Executor.step`` and captured decode step."""
     import torch
     from mrun_b200 import Engine
     from mrun_b200.config import Qwen3Config, ZasesunConfig
     from mrun_b200.config.balivik import BalivikConfig
     from mrun_b200.config.fikudra import FikudraConfig
+    from mrun_b200.config.nisotar import NisotarConfig
     from mrun_b200.engine import StepEntry
     context, batch = 1024, 8
     out = {}
     sampler = ClockSampler()
     sampler.start()
-    size_sets = {"zasesun": DESIGN_SIZES, "balivik": BALIVIK_SIZES, "fikudra": FIKUDRA_SIZES}[args.design]
-    beside = "balivik" if args.design == "fikudra" else "qwen3"
+    size_sets = {"zasesun": DESIGN_SIZES, "balivik": BALIVIK_SIZES, "fikudra": FIKUDRA_SIZES,
+                 "nisotar": NISOTAR_SIZES}[args.design]
+    beside = {"fikudra": "balivik", "nisotar": "fikudra"}.get(args.design, "qwen3")
     for name in (args.sizes.split(",") if args.sizes else sorted(size_sets)):
         z_sizes, q_sizes = size_sets[name]
         row = {}
         for design in (args.design, beside):
             state_bytes = 0
-            if design == "fikudra":
+            if design == "nisotar":
+                config = NisotarConfig.from_dict(z_sizes)
+                vocab, h = z_sizes["vocab"], z_sizes["width"]
+                flops, kv_bytes, state_bytes = nisotar_counts(z_sizes, PREFILL_TOKENS, context)
+            elif design == "fikudra" and args.design == "nisotar":
+                config = FikudraConfig.from_dict(q_sizes)
+                vocab, h = q_sizes["vocab"], q_sizes["width"]
+                flops, kv_bytes, state_bytes = fikudra_counts(q_sizes, PREFILL_TOKENS)
+            elif design == "fikudra":
                 config = FikudraConfig.from_dict(z_sizes)
                 vocab, h = z_sizes["vocab"], z_sizes["width"]
                 flops, kv_bytes, state_bytes = fikudra_counts(z_sizes, PREFILL_TOKENS)
@@ -526,8 +617,8 @@ def main() -> int:
     parser.add_argument("--profiler-range", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                         help="bracket the timed decode steps (or the last timed prefill) with "
                              "cudaProfilerStart/Stop, for a profiler started with --profile-from-start off")
-    parser.add_argument("--design", choices=["zasesun", "balivik", "fikudra"], default=None,
-                        help="instead of the default workload: the named design beside Qwen3 (fikudra: beside Balivik) at equal sizes "
+    parser.add_argument("--design", choices=["zasesun", "balivik", "fikudra", "nisotar"], default=None,
+                        help="instead of the default workload: the named design beside Qwen3 (fikudra: beside Balivik; nisotar: beside Fikudra) at equal sizes "
                              "(prefill of 2,048 tokens, decode at batch 8)")
     parser.add_argument("--sizes", default=None, help="with --design: which of its size sets to run, comma separated")
     args = parser.parse_args()

@@ -116,7 +116,7 @@ def latent_attention(m, W, p, h, eps, positions):
     q = (h @ W[p + "q"].T).view(T, H, D + R)
     down = h @ W[p + "dkv"].T
     c = unit_rms(down[:, :C], eps) * W[p + "dkv.norm"]
-    rot = dict(m["rot"], dims=R)
+    rot = dict(m["rot"], dims=R) if R else None          # the rotated part turns as a whole
     shared = rotate(down[:, C:].view(T, 1, R), positions, rot)
     q_rot = rotate(q[:, :, D:], positions, rot)
     k_plain = (c @ W[p + "uk"].T).view(T, H, D)
