@@ -423,7 +423,9 @@ def _nisotar_sizes(width, heads, kv_heads, att_dim, dim, experts, top, expert_ff
     left = {"heads": heads, "kv_heads": kv_heads, "dim": att_dim, "vdim": att_dim, "scale": att_dim ** -0.5,
             "mask": {"size": 256}, "rot": {"base": 100000.0, "dims": att_dim // 2}}
     right = {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4, "decay_rank": rank, "gate_rank": rank}
-    lat = {"heads": heads, "dim": att_dim, "rot_dim": att_dim // 2, "vdim": att_dim, "kv_rank": 256 - att_dim // 2,
+    # 16 heads over the one latent row at every width: more take the tiled kernel, whose tile list is
+    # made on the host, and a model with it decodes uncaptured
+    lat = {"heads": min(heads, 16), "dim": att_dim, "rot_dim": att_dim // 2, "vdim": att_dim, "kv_rank": 256 - att_dim // 2,
            "scale": (att_dim + att_dim // 2) ** -0.5, "mask": {"size": 384}, "rot": {"base": 10000.0, "dims": att_dim // 2}}
     kinds = [("parallel", {"left": left, "right": right}), ("attention", att), ("latent_attention", lat)]
     moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}}

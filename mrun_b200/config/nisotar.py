@@ -155,6 +155,8 @@ class NisotarConfig:
             raise ConfigError(f"{where}mlp", "is neither an object nor null")
         fw = f"{where}mlp."
         kind = mlp.get("kind")
+        if kind is None:        # left out: what the entry holds says which it is
+            kind = "moe" if "router" in mlp else "dense" if "ff" in mlp else None
         if kind == "dense":
             return ClampedGatedMLPSpec(hidden=width, intermediate=_count(mlp, "ff", fw), limit=_positive(mlp, "limit", fw),
                                        alpha=DENSE_GATE_ALPHA, biases=True)

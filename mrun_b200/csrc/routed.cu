@@ -253,15 +253,16 @@ route_grouped_kernel(const float* __restrict__ logits, long ldz, float* __restri
 template <typename TA, bool EXACT>
 __global__ void clamped_glu_kernel(const TA* __restrict__ u, long ldu, TA* __restrict__ act, long lda,
                                    const float* __restrict__ weights, long ldw, int per_block, long total, int blocks,
-                                   int ff, float limit, float alpha, float up_offset) {
+                                   int ff, float limit, float alpha, float up_offset, const float* __restrict__ bias) {
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long row = i / ((long)blocks * ff);
     const int c = (int)(i - row * blocks * ff);
     const int e = c / ff, j = c - e * ff;
     const TA* base = u + row * ldu + (size_t)e * 2 * ff;
-    const float g = fminf(to_float(base[j]), limit);
-    const float up = fminf(fmaxf(to_float(base[ff + j]), -limit), limit);
+    const float* b = bias ? bias + (size_t)e * 2 * ff : nullptr;
+    const float g = fminf(to_float(base[j]) + (b ? b[j] : 0.f), limit);
+    const float up = fminf(fmaxf(to_float(base[ff + j]) + (b ? b[ff + j] : 0.f), -limit), limit);
     const float w = weights ? (per_block ? weights[row * ldw + e] : weights[row * ldw]) : 1.f;
     float s;
     if constexpr (EXACT) s = 1.f / (1.f + expf(-alpha * g));
@@ -274,7 +275,7 @@ template <typename TA, bool EXACT>
 __global__ void __launch_bounds__(256)
 clamped_glu_vec_kernel(const TA* __restrict__ u, long ldu, TA* __restrict__ act, long lda,
                        const float* __restrict__ weights, long ldw, int per_block, int blocks, int ff, float limit,
-                       float alpha, float up_offset) {
+                       float alpha, float up_offset, const float* __restrict__ bias) {
     const long row = blockIdx.x;
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
     if (c >= blocks * ff) return;
@@ -283,6 +284,13 @@ clamped_glu_vec_kernel(const TA* __restrict__ u, long ldu, TA* __restrict__ act,
     float g[8], up[8];
     Vec8<TA>::load(base + j, g);
     Vec8<TA>::load(base + ff + j, up);
+    if (bias) {         // the biases of the two projections, laid out like a row of u
+        float bg[8], bu[8];
+        Vec8<float>::load(bias + (size_t)e * 2 * ff + j, bg);
+        Vec8<float>::load(bias + (size_t)e * 2 * ff + ff + j, bu);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { g[i] += bg[i]; up[i] += bu[i]; }
+    }
     const float w = weights ? (per_block ? weights[row * ldw + e] : weights[row * ldw]) : 1.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -325,27 +333,28 @@ MRUN_API int mrun_route_grouped(const float* logits, long ldz, float* weights, f
     return 0;
 }
 
-// limit: the clamp of gate and up (infinity: none); up_offset: what is added to up before the product.
+// limit: the clamp of gate and up (infinity: none); up_offset: what is added to up before the product;
+// bias (nullable): float32 [blocks * 2 * ff], added to gate and up before the clamp.
 MRUN_API int mrun_clamped_glu(const void* u, long ldu, void* act, long lda, int act_dtype, const float* weights, long ldw,
                               int per_block, int rows, int blocks, int ff, float limit, float alpha, float up_offset,
-                              cudaStream_t stream) {
+                              const float* bias, cudaStream_t stream) {
     MRUN_REQUIRE(rows >= 0 && blocks > 0 && ff > 0, "clamped_glu: bad sizes rows=%d blocks=%d ff=%d", rows, blocks, ff);
     MRUN_REQUIRE(ldu >= (long)blocks * 2 * ff && lda >= (long)blocks * ff, "clamped_glu: a row stride below the row");
     if (rows == 0) return 0;
     const long total = (long)rows * blocks * ff;
     const unsigned grid = (unsigned)((total + 255) / 256);
     const size_t unit = act_dtype == MRUN_F32 ? 4 : 2;
-    if (ff % 8 == 0 && ((((uintptr_t)u) | ((uintptr_t)act)) & 15) == 0 && (ldu * unit) % 16 == 0 && (lda * unit) % 16 == 0 &&
+    if (ff % 8 == 0 && ((((uintptr_t)u) | ((uintptr_t)act) | ((uintptr_t)bias)) & 15) == 0 && (ldu * unit) % 16 == 0 && (lda * unit) % 16 == 0 &&
         rows <= 0x7fffffff) {
         const dim3 vec_grid(rows, (blocks * ff / 8 + 255) / 256);
         if (act_dtype == MRUN_F32)
             clamped_glu_vec_kernel<float, true><<<vec_grid, 256, 0, stream>>>((const float*)u, ldu, (float*)act, lda, weights,
                                                                                ldw, per_block, blocks, ff, limit, alpha,
-                                                                               up_offset);
+                                                                               up_offset, bias);
         else if (act_dtype == MRUN_BF16)
             clamped_glu_vec_kernel<__nv_bfloat16, false><<<vec_grid, 256, 0, stream>>>(
                 (const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)act, lda, weights, ldw, per_block, blocks, ff, limit, alpha,
-                up_offset);
+                up_offset, bias);
         else
             return mrun_set_error("clamped_glu: unknown dtype code %d", act_dtype);
         MRUN_CHECK_LAUNCH("clamped_glu");
@@ -353,11 +362,11 @@ MRUN_API int mrun_clamped_glu(const void* u, long ldu, void* act, long lda, int 
     }
     if (act_dtype == MRUN_F32)
         clamped_glu_kernel<float, true><<<grid, 256, 0, stream>>>((const float*)u, ldu, (float*)act, lda, weights, ldw,
-                                                                   per_block, total, blocks, ff, limit, alpha, up_offset);
+                                                                   per_block, total, blocks, ff, limit, alpha, up_offset, bias);
     else if (act_dtype == MRUN_BF16)
         clamped_glu_kernel<__nv_bfloat16, false><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)act,
                                                                             lda, weights, ldw, per_block, total, blocks, ff,
-                                                                            limit, alpha, up_offset);
+                                                                            limit, alpha, up_offset, bias);
     else
         return mrun_set_error("clamped_glu: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("clamped_glu");

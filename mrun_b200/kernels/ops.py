@@ -1252,12 +1252,14 @@ def table_route(token_ids: torch.Tensor, table: torch.Tensor, experts: int, chos
 
 
 def clamped_glu(u: torch.Tensor, weights: Optional[torch.Tensor], blocks: int, ff: int, limit: float, alpha: float,
-                up_offset: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                up_offset: float = 1.0, out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``u``: [rows, blocks * 2 * ff], a block of [gate | up] columns per expert.  Returns [rows,
     blocks * ff]: g * sigmoid(alpha * g) * (clamp(up, +-limit) + up_offset) with g = min(gate,
     limit), times ``weights[row, block]`` (float32 [rows, blocks]) or ``weights[row]`` (float32
     [rows]).  ``limit`` infinite: no clamp (alpha = 1 and up_offset = 0: SiLU(gate) * up).  ``u``,
-    ``weights`` and ``out`` may be column slices of wider matrices."""
+    ``weights`` and ``out`` may be column slices of wider matrices.  ``bias`` (float32, laid out like a
+    row of ``u``) is added to gate and up before the clamp: the projections' biases, never rounded
+    into ``u``."""
     ldu = _strided_rows(u, "u")
     rows = u.shape[0]
     if u.shape[1] != blocks * 2 * ff:
@@ -1273,6 +1275,10 @@ def clamped_glu(u: torch.Tensor, weights: Optional[torch.Tensor], blocks: int, f
             ldw = weights.stride(0)
         else:
             raise KernelError(f"clamped_glu: weights {tuple(weights.shape)}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.numel() != blocks * 2 * ff:
+            raise KernelError(f"clamped_glu: bias has {bias.numel()} entries, a row has {blocks * 2 * ff}")
     if out is None:
         out = torch.empty((rows, blocks * ff), dtype=u.dtype, device=u.device)
     lda = _strided_rows(out, "out")
@@ -1280,7 +1286,7 @@ def clamped_glu(u: torch.Tensor, weights: Optional[torch.Tensor], blocks: int, f
         raise KernelError(f"clamped_glu: out is {tuple(out.shape)} {out.dtype}")
     _lib.core().call("mrun_clamped_glu", _ptr(u), _c_long(ldu), _ptr(out), _c_long(lda), dtype_code(u.dtype), _ptr(weights),
                      _c_long(ldw), _c_int(per_block), _c_int(rows), _c_int(blocks), _c_int(ff), _c_float(limit),
-                     _c_float(alpha), _c_float(up_offset), _stream())
+                     _c_float(alpha), _c_float(up_offset), _ptr(bias), _stream())
     return out
 
 

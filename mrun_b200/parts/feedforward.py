@@ -83,8 +83,8 @@ class GatedMLP:
 @register_feed_forward("clamped_gated_mlp")
 class ClampedGatedMLP:
     """Dense gated feed-forward with clamped branches (the formulas are with
-    :class:`ClampedGatedMLPSpec`): one product makes [gate | up] with their biases,
-    ``ops.clamped_glu`` applies min / clamp, the gate's sigmoid and the +1, one product goes down
+    :class:`ClampedGatedMLPSpec`): one product makes [gate | up], ``ops.clamped_glu`` adds their
+    biases in 32-bit and applies min / clamp, the gate's sigmoid and the +1, one product goes down
     with its bias.  The checkpoint names the matrices ``gate``, ``up``, ``down`` and their biases
     ``gate.b``, ``up.b``, ``down.b``."""
 
@@ -114,8 +114,8 @@ class ClampedGatedMLP:
 
     def forward(self, x, ctx, defer_output: bool = False):
         s = self.spec
-        u = ops.linear(x, self.w_gate_up, bias=self.b_gate_up)
-        act = ops.clamped_glu(u, None, 1, s.intermediate, s.limit, s.alpha)
+        u = ops.linear(x, self.w_gate_up)
+        act = ops.clamped_glu(u, None, 1, s.intermediate, s.limit, s.alpha, bias=self.b_gate_up)
         if defer_output:
             return ops.linear_or_pending(act, self.w_down, self.b_down)
         return ops.linear(act, self.w_down, bias=self.b_down)
