@@ -1,4 +1,5 @@
-// Layer norm without a bias fused with the residual sum, and the mean of two RMS-normed branches.
+// Layer norm without a bias fused with the residual sum, the mean of two RMS-normed branches, and
+// the two as one kernel.
 //
 // All arithmetic is 32-bit; a row is one block of 256 threads whatever the batch, so the order of
 // additions depends on the width only.
@@ -145,6 +146,53 @@ pair_norm_mean_kernel(const float* __restrict__ a, const float* __restrict__ b, 
         out[row + h] = share * (a[row + h] * ia * wa[h] + b[row + h] * ib * wb[h]);
 }
 
+// ------------------------------------------------------------------------------------------
+// The two steps above as one: v = resid + share * (rmsnorm(a) * wa + rmsnorm(b) * wb), then the
+// layer norm of v with `weight`.  rows == null: resid = v (the stream advances); with `rows` the
+// kernel reads row rows[r] of resid, a and b and leaves the stream as it is.  The row is staged
+// in shared memory.
+// ------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(256)
+pair_norm_add_layernorm_kernel(float* __restrict__ resid, const float* __restrict__ a, const float* __restrict__ b,
+                               const float* __restrict__ wa, const float* __restrict__ wb, float eps_pair, float share,
+                               const float* __restrict__ weight, float eps, TA* __restrict__ out,
+                               const int* __restrict__ rows, int hidden) {
+    extern __shared__ float row_buf[];
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    float sa = 0.f, sb = 0.f;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        const float x = a[src + h], y = b[src + h];
+        sa += x * x;
+        sb += y * y;
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float ia = rsqrtf(sa / (float)hidden + eps_pair), ib = rsqrtf(sb / (float)hidden + eps_pair);
+    float s = 0.f;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        const float v = resid[src + h] + share * (a[src + h] * ia * wa[h] + b[src + h] * ib * wb[h]);
+        row_buf[h] = v;
+        s += v;
+    }
+    const float mu = block_sum(s, scratch) / (float)hidden;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        const float d = row_buf[h] - mu;
+        ss += d * d;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+    TA* dst = out + (size_t)r * hidden;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        const float v = row_buf[h];
+        if (!rows) resid[src + h] = v;
+        dst[h] = from_float<TA>((v - mu) * inv * weight[h]);
+    }
+}
+
 }  // namespace
 
 // delta_dtype: the type of `delta` (MRUN_F32, or the activation type `act_dtype`).
@@ -176,5 +224,32 @@ MRUN_API int mrun_pair_norm_mean(const float* a, const float* b, const float* wa
     if (rows == 0) return 0;
     pair_norm_mean_kernel<<<rows, 256, 0, stream>>>(a, b, wa, wb, eps, share, out, hidden);
     MRUN_CHECK_LAUNCH("pair_norm_mean");
+    return 0;
+}
+
+MRUN_API int mrun_pair_norm_add_layernorm(float* resid, const float* a, const float* b, const float* wa, const float* wb,
+                                          float eps_pair, float share, const float* weight, float eps, void* out,
+                                          int act_dtype, const int* rows, int n_rows, int hidden, cudaStream_t stream) {
+    MRUN_REQUIRE(n_rows >= 0 && hidden > 0, "pair_norm_add_layernorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    MRUN_REQUIRE((size_t)hidden * sizeof(float) <= 200 * 1024, "pair_norm_add_layernorm: hidden=%d exceeds the supported 51200",
+                 hidden);
+    if (n_rows == 0) return 0;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (act_dtype == MRUN_F32) {
+        if (smem > 48 * 1024)
+            MRUN_CHECK_CUDA(cudaFuncSetAttribute(pair_norm_add_layernorm_kernel<float>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "pair_norm_add_layernorm");
+        pair_norm_add_layernorm_kernel<float><<<n_rows, 256, smem, stream>>>(resid, a, b, wa, wb, eps_pair, share, weight, eps,
+                                                                             (float*)out, rows, hidden);
+    } else if (act_dtype == MRUN_BF16) {
+        if (smem > 48 * 1024)
+            MRUN_CHECK_CUDA(cudaFuncSetAttribute(pair_norm_add_layernorm_kernel<__nv_bfloat16>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "pair_norm_add_layernorm");
+        pair_norm_add_layernorm_kernel<__nv_bfloat16><<<n_rows, 256, smem, stream>>>(resid, a, b, wa, wb, eps_pair, share, weight,
+                                                                                     eps, (__nv_bfloat16*)out, rows, hidden);
+    } else {
+        return mrun_set_error("pair_norm_add_layernorm: unknown dtype code %d", act_dtype);
+    }
+    MRUN_CHECK_LAUNCH("pair_norm_add_layernorm");
     return 0;
 }

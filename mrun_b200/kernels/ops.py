@@ -113,6 +113,28 @@ def pair_norm_mean(a: torch.Tensor, b: torch.Tensor, weight_a: torch.Tensor, wei
     return out
 
 
+def pair_norm_add_layernorm(resid: torch.Tensor, pending, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """resid += share * (rmsnorm(a) * weight_a + rmsnorm(b) * weight_b) for a :class:`PendingPairNorm`,
+    then out = layer norm of resid with ``weight``; with ``rows`` only those rows are worked on and
+    resid is left as it is."""
+    _check(resid, "resid", torch.float32); _check(weight, "weight", torch.float32); _check(out, "out")
+    for name, t in (("a", pending.a), ("b", pending.b), ("weight_a", pending.weight_a), ("weight_b", pending.weight_b)):
+        _check(t, name, torch.float32)
+    hidden = resid.shape[-1]
+    n_rows = resid.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    if pending.a.shape != resid.shape or pending.b.shape != resid.shape or weight.numel() != hidden \
+            or pending.weight_a.numel() != hidden or pending.weight_b.numel() != hidden or out.shape != (n_rows, hidden):
+        raise KernelError(f"pair_norm_add_layernorm: resid {tuple(resid.shape)}, a {tuple(pending.a.shape)}, "
+                          f"b {tuple(pending.b.shape)}, out {tuple(out.shape)}")
+    _lib.core().call("mrun_pair_norm_add_layernorm", _ptr(resid), _ptr(pending.a), _ptr(pending.b), _ptr(pending.weight_a),
+                     _ptr(pending.weight_b), _c_float(pending.eps), _c_float(pending.share), _ptr(weight), _c_float(eps),
+                     _ptr(out), dtype_code(out.dtype), _ptr(rows), _c_int(n_rows), _c_int(hidden), _stream())
+    return out
+
+
 def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor,
                  magnitude: float = 1.0) -> torch.Tensor:
     """out[t, j] = magnitude * (cos, sin)(positions[t] * inv_freq[j]); inv_freq is float64."""
@@ -416,7 +438,26 @@ class PendingPostNorm:
         return addend.to(self.act)
 
 
-PENDING = (PendingLinear, PendingPostNorm)      # what a block may hand to the norm after it unadded
+class PendingPairNorm:
+    """Two branch outputs (float32 rows) that join the stream as ``share * (rmsnorm(a) * weight_a +
+    rmsnorm(b) * weight_b)`` and have not been combined yet: a layer norm that follows norms both,
+    adds them and norms the new rows in one kernel (:func:`pair_norm_add_layernorm`).
+    :meth:`compute` makes the addend itself (float32)."""
+
+    def __init__(self, a: torch.Tensor, b: torch.Tensor, weight_a: torch.Tensor, weight_b: torch.Tensor, eps: float,
+                 share: float):
+        self.a, self.b, self.weight_a, self.weight_b = a, b, weight_a, weight_b
+        self.eps, self.share = float(eps), float(share)
+
+    @property
+    def shape(self):
+        return self.a.shape
+
+    def compute(self) -> torch.Tensor:
+        return pair_norm_mean(self.a, self.b, self.weight_a, self.weight_b, self.eps, self.share)
+
+
+PENDING = (PendingLinear, PendingPostNorm, PendingPairNorm)      # what a block may hand to the norm after it unadded
 
 
 def _normed(x):

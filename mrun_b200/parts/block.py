@@ -127,7 +127,9 @@ class SandwichBlock:
         """The branch output as 32-bit rows, with the post-norm that it still has to pass."""
         if isinstance(y, ops.PendingLinear):
             y = ops.linear(y.x, y.w, out_dtype=torch.float32)
-        elif y.dtype != torch.float32:
+        elif isinstance(y, ops.PENDING):
+            y = y.compute()
+        if y.dtype != torch.float32:
             y = y.to(torch.float32)
         return ops.PendingPostNorm(y, post_norm.weight, post_norm.eps, self.scale, self.act)
 

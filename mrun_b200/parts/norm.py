@@ -43,6 +43,8 @@ class RMSNorm:
             out = torch.empty(resid.shape, dtype=self.act, device=resid.device)
             return ops.post_norm_add(resid, delta.branch, delta.weight, delta.scale, delta.eps, self.weight,
                                      self.eps, out)
+        if isinstance(delta, ops.PendingPairNorm):
+            delta = delta.compute().to(self.act)        # no fused form with this norm: the addend, in the activation type
         if isinstance(delta, ops.PendingLinear):
             if ops.norm_fusable(delta, resid, self.weight):
                 return ops.linear_into_norm(delta, resid, self.weight, self.eps)
@@ -59,6 +61,8 @@ class RMSNorm:
             out = torch.empty((rows.numel(), self.size), dtype=self.act, device=resid.device)
             return ops.post_norm_add(resid, delta.branch, delta.weight, delta.scale, delta.eps, self.weight,
                                      self.eps, out, rows=rows)
+        if isinstance(delta, ops.PendingPairNorm):
+            delta = delta.compute().to(self.act)
         if isinstance(delta, ops.PendingLinear):
             delta = delta.compute()
         out = torch.empty((rows.numel(), self.size), dtype=self.act, device=resid.device)
@@ -99,13 +103,17 @@ class LayerNorm:
         return delta
 
     def add_forward(self, resid: torch.Tensor, delta):
-        delta = self._settle(resid, delta, True)
         out = torch.empty(resid.shape, dtype=self.act, device=resid.device)
+        if isinstance(delta, ops.PendingPairNorm):      # two branches still to be normed and averaged: one kernel
+            return ops.pair_norm_add_layernorm(resid, delta, self.weight, self.eps, out)
+        delta = self._settle(resid, delta, True)
         return ops.add_layernorm(resid, delta, self.weight, self.eps, out)
 
     def rows_forward(self, resid: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
-        delta = self._settle(resid, delta, False)
         out = torch.empty((rows.numel(), self.size), dtype=self.act, device=resid.device)
+        if isinstance(delta, ops.PendingPairNorm):
+            return ops.pair_norm_add_layernorm(resid, delta, self.weight, self.eps, out, rows=rows)
+        delta = self._settle(resid, delta, False)
         return ops.add_layernorm(resid, delta, self.weight, self.eps, out, rows=rows)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

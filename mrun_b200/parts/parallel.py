@@ -3,9 +3,12 @@
 Both read the same normed rows.  Each runs as it would alone, with its own kinds of cache: the
 schedule entry's need is the two needs together (at most one of them paged; fixed-size states
 under different names), and both see the entry's one :class:`EntryCache`, of which each uses its
-own members.  Their last products write 32-bit sums; one kernel divides each branch by its root
-mean square over the model width, multiplies it by its weight and takes ``share`` of their sum
-(``ops.pair_norm_mean``).  The result is 32-bit and joins the stream in the next norm's kernel.
+own members.  Their last products write 32-bit sums; each branch is divided by its root mean
+square over the model width, multiplied by its weight, and ``share`` of their sum joins the
+stream.  A caller that takes pending outputs (``defer_output=True``) gets the two branches as
+they are (``ops.PendingPairNorm``): a layer norm behind it does the branch norms, the average,
+the residual sum and its own norm in one kernel; otherwise ``ops.pair_norm_mean`` makes the
+32-bit addend.
 """
 from __future__ import annotations
 
@@ -19,6 +22,8 @@ from .base import MIXERS, Runtime, local, register_mixer
 
 @register_mixer("parallel")
 class ParallelMixer:
+    can_defer_output = True         # ``forward(..., defer_output=True)`` may return ``ops.PendingPairNorm``
+
     @staticmethod
     def tensor_specs(spec: ParallelMixerSpec, prefix: str):
         out = []
@@ -65,8 +70,9 @@ class ParallelMixer:
             y = y.compute()
         return y if y.dtype == torch.float32 else y.to(torch.float32)
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, defer_output: bool = False):
         (left, w_left, left_defers), (right, w_right, right_defers) = self.sides
         a = self._branch(left, left_defers, x, ctx, cache)
         b = self._branch(right, right_defers, x, ctx, cache)
-        return ops.pair_norm_mean(a, b, w_left, w_right, self.spec.eps, self.spec.share)
+        pending = ops.PendingPairNorm(a, b, w_left, w_right, self.spec.eps, self.spec.share)
+        return pending if defer_output else pending.compute()

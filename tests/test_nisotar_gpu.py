@@ -61,6 +61,36 @@ def test_pair_norm_mean_kernel(hidden):
     close(got, want, "float32", "pair norm", bound=1e-5)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [8, 100, 1024, 13000])
+def test_pair_norm_add_layernorm_kernel(dtype, hidden):
+    """The two branch norms, their average, the residual sum and the layer norm as one kernel: the
+    stream advances by the addend and the normed rows are the plain ones; at chosen rows the stream
+    stays."""
+    from mrun_b200.kernels import ops
+    act = getattr(torch, dtype)
+    gen = torch.Generator().manual_seed(hidden + 1)
+    resid = torch.randn(9, hidden, generator=gen) * 2 - 20.0
+    a, b = torch.randn(9, hidden, generator=gen) * 3, torch.randn(9, hidden, generator=gen) * 0.01
+    wa, wb = 1 + 0.3 * torch.randn(hidden, generator=gen), 0.5 * torch.randn(hidden, generator=gen)
+    w = 1 + 0.3 * torch.randn(hidden, generator=gen)
+    addend = 0.5 * (plain.unit_rms(a.double(), 1e-6) * wa.double() + plain.unit_rms(b.double(), 1e-6) * wb.double())
+    want = plain.layer_norm(resid.double() + addend, w.double(), 1e-5)
+    pending = ops.PendingPairNorm(a.to(DEV), b.to(DEV), wa.to(DEV), wb.to(DEV), 1e-6, 0.5)
+    close(pending.compute(), addend, "float32", "the addend alone", bound=1e-5)
+    stream = resid.to(DEV)
+    out = torch.empty((9, hidden), dtype=act, device=DEV)
+    ops.pair_norm_add_layernorm(stream, pending, w.to(DEV), 1e-5, out)
+    close(out, want, dtype, "all rows", bound=2e-5 if dtype == "float32" else 1e-2)
+    assert torch.allclose(stream.cpu().double(), resid.double() + addend, atol=1e-5)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32)
+    stream = resid.to(DEV)
+    out = torch.empty((3, hidden), dtype=act, device=DEV)
+    ops.pair_norm_add_layernorm(stream, pending, w.to(DEV), 1e-5, out, rows=rows.to(DEV))
+    close(out, want[rows.long()], dtype, "chosen rows", bound=2e-5 if dtype == "float32" else 1e-2)
+    assert torch.equal(stream.cpu(), resid)
+
+
 @pytest.mark.parametrize("experts, top", [(3, 1), (8, 3), (16, 16), (40, 5), (130, 7), (300, 2)])
 @pytest.mark.parametrize("bias", [False, True])
 def test_route_by_logits_kernel(experts, top, bias):
@@ -226,6 +256,7 @@ LATENT_SHAPES = [  # heads, plain size, rotated size, value size, latent size, w
     (5, 16, 0, 8, 32, 100000, 16),      # no rotated part, a window longer than every request
     (20, 16, 16, 24, 112, 33, 16),      # twenty query heads over the one latent row
     (2, 64, 32, 64, 96, 1, 8),          # a window of one position
+    (3, 48, 16, 40, 128, 27, 16),       # a row of 144 features
 ]
 
 
@@ -305,6 +336,20 @@ def test_parallel_mixer_alone(dtype, tensor_cores, left, right, page, monkeypatc
         assert 0.2 < float(lone.norm() / full.norm()) < 5.0
         return full
     check_rows(lambda rows, ctx, caches: part.forward(rows, ctx, caches[0]), hidden, dtype, LENGTHS, fn, [part.cache_need()], rt)
+    # left pending for the layer norm behind it: the branch norms, the average, the sum into a stream
+    # of zeros and the norm are one kernel
+    from mrun_b200.config.spec import LayerNormSpec
+    from mrun_b200.kernels import ops
+    from mrun_b200.parts import NORMS
+    norm_weight = (1 + 0.2 * torch.randn(hidden, generator=gen)).to(torch.bfloat16).float()
+    norm = NORMS.build(LayerNormSpec(hidden, 1e-5, bare=True), {"": norm_weight}, rt)
+
+    def through_norm(rows, ctx, caches):
+        pending = part.forward(rows, ctx, caches[0], defer_output=True)
+        assert isinstance(pending, ops.PendingPairNorm)
+        return norm.add_forward(torch.zeros((rows.shape[0], hidden), dtype=torch.float32, device=DEV), pending)
+    check_rows(through_norm, hidden, dtype, LENGTHS, lambda h, _: plain.layer_norm(fn(h, _), norm_weight.double(), 1e-5),
+               [part.cache_need()], rt)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
