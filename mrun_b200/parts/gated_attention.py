@@ -7,8 +7,10 @@ One product makes [q | k | v | gate] (or [q | gate] for a layer that reads anoth
 [q | k] for one whose values are its keys); ``ops.proj_norm_rope_cache`` or
 ``ops.head_norm_rope_cache`` norms q and k, rotates them and writes k and v into the pages; the
 attention kernel applies the sink and the gate's sigmoid to every head's output; the output
-projection follows.  Scores, softmax, the sink and the gate are 32-bit in both precisions.  A
-chunked mask reaches the attention kernels as a negative window (minus the chunk's size).
+projection follows.  In a step of single tokens the tensor-core decode kernels take the rows of
+a layer with a norm per head raw and do the norm, the rotation and the page write themselves, as
+they do for :class:`Attention`.  Scores, softmax, the sink and the gate are 32-bit in both
+precisions.  A chunked mask reaches the attention kernels as a negative window (minus the chunk's size).
 
 Kernels: bfloat16 with keys and values of one size that the tensor-core attention takes go
 through the framework's paged kernels (tcgen05 prompt tiles, TMA decode; the sink enters their
@@ -24,7 +26,7 @@ import torch
 from ..cache.needs import PagedKV
 from ..config.spec import GatedAttentionSpec, TensorSpec
 from ..kernels import ops
-from ..kernels.attention import paged_attention, supports_tensor_cores
+from ..kernels.attention import decode_fuses_input, paged_attention, supports_tensor_cores
 from .base import POSITIONS, Runtime, register_mixer
 
 
@@ -98,6 +100,10 @@ class GatedAttention:
                              and supports_tensor_cores(runtime.precision.act, spec.dim, ratio))
         # the tiled kernel that very wide groups fall to needs a tile list made on the host
         self.graph_safe = not (self.tensor_cores and ratio > 16)
+        # rows laid out [q | k | v] with a norm per head and half-split pairs are what the decode
+        # attention kernels take raw (they norm, rotate and store the step's q, k and v themselves)
+        self.fusable = (self.tensor_cores and spec.qk_norm == "head" and spec.own_kv and not self.keys_as_values
+                        and self.pairing == "half")
 
     def cache_need(self):
         s = self.spec
@@ -122,6 +128,17 @@ class GatedAttention:
         y = ops.linear(x, self.w_in)
         rot = self.position.rotation(ctx) if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
+        gate = y[:, self.gate_off:self.gate_off + s.heads] if s.head_gate else None
+        out = torch.empty((x.shape[0], s.heads * s.vdim), dtype=x.dtype, device=x.device)
+        if self.fusable and decode_fuses_input(ctx, x.dtype, s.heads, s.kv_heads, s.dim, self.runtime.page_size):
+            # a pure decode step: the attention kernel norms, rotates and stores q, k, v itself
+            paged_attention(y, y.stride(0), out, cache, group, ctx, s.heads, s.softmax_scale, self.mask, sink=s.sink,
+                            raw=(self.q_weight, self.k_weight, s.eps, rot, rotary_dim, group.slot_mapping))
+            if gate is not None:
+                ops.head_gate(out, gate, s.heads)
+            if defer_output:
+                return ops.linear_or_pending(out, self.w_o)
+            return ops.linear(out, self.w_o)
         if self.per_head:
             ops.head_norm_rope_cache(y, 0, max(self.k_off, 0), self.v_off, s.heads, s.kv_heads, s.dim, s.vdim,
                                      self.q_weight, self.k_weight, s.eps, rot, rotary_dim, self.pairing,
@@ -130,8 +147,6 @@ class GatedAttention:
             ops.proj_norm_rope_cache(y, 0, self.k_off, self.v_off, s.heads, s.kv_heads, s.dim, s.vdim, self.q_weight,
                                      self.k_weight, s.eps, rot, rotary_dim, self.pairing,
                                      group.slot_mapping if s.own_kv else None, cache.k, cache.v, self.runtime.page_size)
-        gate = y[:, self.gate_off:self.gate_off + s.heads] if s.head_gate else None
-        out = torch.empty((x.shape[0], s.heads * s.vdim), dtype=x.dtype, device=x.device)
         if self.tensor_cores:
             paged_attention(y, y.stride(0), out, cache, group, ctx, s.heads, s.softmax_scale, self.mask, sink=s.sink)
             if gate is not None:
