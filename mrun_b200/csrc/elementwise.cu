@@ -825,6 +825,101 @@ __global__ void head_norm_rope_cache_kernel(TA* __restrict__ x, long ld, long q_
     }
 }
 
+// The same for bfloat16 heads of 16, 32, 64, 128 or 256 features with keys and values of one size,
+// half-split pairs and a rotating part that is a multiple of 16 features (or none): LANES = dim / 8
+// lanes share a head, eight values (16 bytes) a lane, so a row is read and written in whole 16-byte
+// pieces; the sum of squares and the rotation's partner values (the lane rotary_dim / 16 further
+// along holds j + rotary_dim / 2) travel by shuffles.  The arithmetic is the scalar kernel's, value
+// by value.
+template <int LANES>
+__global__ void __launch_bounds__(128)
+head_norm_rope_cache_vec_kernel(__nv_bfloat16* __restrict__ x, long ld, long q_off, long k_off, long v_off,
+                                const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                                const float2* __restrict__ rot, int rotary_dim, const int* __restrict__ slots,
+                                __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int tokens,
+                                int heads, int kv_heads, int page_size) {
+    constexpr int dim = LANES * 8;
+    const int sub = threadIdx.x % LANES;                       // this lane's place in its head
+    const int per_token = heads + (v_off >= 0 ? 2 : 1) * kv_heads;
+    const long item = ((long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;
+    // lanes of a group leave together: the shuffles below name the group's lanes only
+    const unsigned lane = threadIdx.x & 31;
+    const unsigned group_mask = LANES == 32 ? 0xffffffffu : (((1u << LANES) - 1u) << (lane / LANES * LANES));
+    if (item >= (long)tokens * per_token) return;
+    const int t = (int)(item / per_token), slot_head = (int)(item - (long)t * per_token);
+    const bool is_q = slot_head < heads;
+    const bool is_k = !is_q && slot_head < heads + kv_heads;
+    const int slot = slots ? slots[t] : -1;
+    if (!is_q && slot < 0) return;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
+    __nv_bfloat16* row = x + (size_t)t * ld;
+    if (!is_q && !is_k) {       // a value head of a projection of its own: plain copy
+        const int g = slot_head - heads - kv_heads;
+        const uint4* src = reinterpret_cast<const uint4*>(row + v_off + (size_t)g * dim);
+        uint4* dst = reinterpret_cast<uint4*>(v_cache + (((size_t)page * kv_heads + g) * page_size + off) * dim);
+        dst[sub] = src[sub];
+        return;
+    }
+    const int g = is_q ? slot_head : slot_head - heads;
+    __nv_bfloat16* src = row + (is_q ? q_off : k_off) + (size_t)g * dim;
+    __nv_bfloat16* dst = is_q ? src : k_cache + (((size_t)page * kv_heads + g) * page_size + off) * dim;
+    const uint4 raw = reinterpret_cast<const uint4*>(src)[sub];
+    if (is_k && v_off < 0)      // the values are the keys as projected
+        reinterpret_cast<uint4*>(v_cache + (((size_t)page * kv_heads + g) * page_size + off) * dim)[sub] = raw;
+    float v[8];
+    {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+    const float* weight = is_q ? q_weight : k_weight;
+    if (weight) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+#pragma unroll
+        for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(group_mask, ss, o);
+        const float inv = rsqrtf(ss / (float)dim + eps);
+        float w[8];
+        Vec8<float>::load(weight + sub * 8, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * w[i];
+    }
+    if (rot && rotary_dim > 0) {
+        const int hop = rotary_dim / 16;                       // lanes between a feature and its partner
+        const bool first = sub < hop, second = !first && sub < 2 * hop;
+        // every lane of the group takes part in the shuffles; lanes beyond the rotating part keep their values
+        const int partner = first ? sub + hop : (second ? sub - hop : sub);
+        float other[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) other[i] = __shfl_sync(group_mask, v[i], (lane / LANES) * LANES + partner);
+        if (first || second) {
+            const float2* cs = rot + (size_t)t * (rotary_dim >> 1) + (first ? sub : sub - hop) * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 c = cs[i];
+                v[i] = first ? v[i] * c.x - other[i] * c.y : v[i] * c.x + other[i] * c.y;
+            }
+        }
+    }
+    Vec8<__nv_bfloat16>::store(dst + sub * 8, v);
+}
+
+template <int LANES>
+static void launch_head_norm_rope_cache_vec(void* x, long ld, long q_off, long k_off, long v_off, const float* q_weight,
+                                            const float* k_weight, float eps, const float* rot, int rotary_dim,
+                                            const int* slots, void* k_cache, void* v_cache, int tokens, int heads,
+                                            int kv_heads, int page_size, cudaStream_t stream) {
+    const long items = (long)tokens * (heads + (v_off >= 0 ? 2 : 1) * kv_heads);
+    const long threads = items * LANES;
+    head_norm_rope_cache_vec_kernel<LANES><<<(unsigned)((threads + 127) / 128), 128, 0, stream>>>(
+        (__nv_bfloat16*)x, ld, q_off, k_off, v_off, q_weight, k_weight, eps, (const float2*)rot, rotary_dim, slots,
+        (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens, heads, kv_heads, page_size);
+}
+
 MRUN_API int mrun_head_norm_rope_cache(void* x, long ld, long q_off, long k_off, long v_off, int act_dtype,
                                        const float* q_weight, const float* k_weight, float eps, const float* rot,
                                        int rotary_dim, int pairing, const int* slots, void* k_cache, void* v_cache,
@@ -846,6 +941,25 @@ MRUN_API int mrun_head_norm_rope_cache(void* x, long ld, long q_off, long k_off,
     const unsigned blocks = (unsigned)((items + warps - 1) / warps);
     const size_t smem = (size_t)warps * dim * sizeof(float);
     if (slots == nullptr) k_cache = v_cache = nullptr;
+    const bool aligned = ((((uintptr_t)x) | ((uintptr_t)k_cache) | ((uintptr_t)v_cache) | ((uintptr_t)q_weight) |
+                           ((uintptr_t)k_weight)) & 15) == 0 &&
+                         ld % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && (v_off < 0 || v_off % 8 == 0);
+    if (act_dtype == MRUN_BF16 && aligned && dim == vdim && pairing == 0 && rotary_dim % 16 == 0 &&
+        (dim == 16 || dim == 32 || dim == 64 || dim == 128 || dim == 256)) {
+#define MRUN_HEAD_VEC(L)                                                                                              \
+    launch_head_norm_rope_cache_vec<L>(x, ld, q_off, k_off, v_off, q_weight, k_weight, eps, rot, rot ? rotary_dim : 0, \
+                                       slots, k_cache, v_cache, tokens, heads, kv_heads, page_size, stream)
+        switch (dim) {
+            case 16: MRUN_HEAD_VEC(2); break;
+            case 32: MRUN_HEAD_VEC(4); break;
+            case 64: MRUN_HEAD_VEC(8); break;
+            case 128: MRUN_HEAD_VEC(16); break;
+            default: MRUN_HEAD_VEC(32); break;
+        }
+#undef MRUN_HEAD_VEC
+        MRUN_CHECK_LAUNCH("head_norm_rope_cache");
+        return 0;
+    }
     if (act_dtype == MRUN_F32)
         head_norm_rope_cache_kernel<float><<<blocks, warps * 32, smem, stream>>>(
             (float*)x, ld, q_off, k_off, v_off, q_weight, k_weight, eps, (const float2*)rot, rotary_dim, pairing, slots,

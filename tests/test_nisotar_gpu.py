@@ -118,16 +118,19 @@ def test_route_by_logits_kernel(experts, top, bias):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, rot_dims, pairing, own_values",
                          [(4, 2, 32, 32, 16, "half", False), (3, 3, 20, 12, 20, "half", True), (6, 1, 64, 64, 0, "half", False),
-                          (2, 2, 24, 40, 8, "interleaved", True), (5, 1, 130, 130, 64, "half", False)])
+                          (2, 2, 24, 40, 8, "interleaved", True), (5, 1, 130, 130, 64, "half", False),
+                          (3, 1, 128, 128, 64, "half", True), (2, 2, 256, 256, 256, "half", False), (4, 4, 16, 16, 16, "half", True),
+                          (2, 1, 64, 64, 8, "half", True), (2, 1, 64, 64, 32, "interleaved", False)])
 def test_head_norm_rope_cache_kernel(dtype, heads, kv_heads, dim, vdim, rot_dims, pairing, own_values):
     """q normed and rotated in place; the pages get the normed, rotated keys and the values: a
-    projection of their own, or the keys as they came in."""
+    projection of their own, or the keys as they came in.  Heads of 16 to 256 features in rows that
+    start on 16 bytes take the kernel that moves 16 bytes a lane, the others an element a lane."""
     from mrun_b200.kernels import ops
     act = getattr(torch, dtype)
     gen = torch.Generator().manual_seed(dim)
     tokens, page = 11, 4
     nq, nk, nv = heads * dim, kv_heads * dim, kv_heads * vdim
-    width = nq + nk + (nv if own_values else 0) + 3
+    width = nq + nk + (nv if own_values else 0) + (8 if dim % 8 == 0 else 3)
     x = (torch.randn(tokens, width, generator=gen) * 2).to(act)
     wq, wk = 1 + 0.3 * torch.randn(dim, generator=gen), 1 + 0.3 * torch.randn(dim, generator=gen)
     positions = torch.arange(tokens) * 7
