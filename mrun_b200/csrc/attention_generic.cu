@@ -2,7 +2,8 @@
 //
 // This is the attention of the whole-model 32-bit path, and the kernel that takes the shapes the
 // tensor-core kernels refuse.  One block per (token, query head).  A token at position p of its
-// request sees keys lo..p, lo = 0 or p - window + 1, read from the request's pages; the keys of
+// request sees keys lo..p, lo = 0, p - window + 1, or the start of p's chunk for a window of minus
+// the chunk's size (first_visible()), read from the request's pages; the keys of
 // the tokens in this step are already in the pages when it runs.  Scores, softmax and the
 // weighted sum are 32-bit; keys are consumed in tiles of 128 in position order, so the result of
 // a token depends on its own keys only, not on the batch around it.

@@ -13,8 +13,9 @@
 //    outputs with their running max and sum).
 //
 // Both read keys and values from the pages (cache[page, kv_head, offset, :]) through the block
-// table of the token's state slot.  A token at position p sees keys lo..p, lo = 0 or
-// p - window + 1.  Keys outside that range, and pages that were given back, are never
+// table of the token's state slot.  A token at position p sees keys lo..p, lo = 0,
+// p - window + 1, or the start of p's chunk for a window of minus the chunk's size
+// (first_visible()).  Keys outside that range, and pages that were given back, are never
 // dereferenced: their tile rows are zero-filled.
 //
 // Math as in the CUDA-core kernel: s = scale * q·k, softmax in 32-bit, o = p·v

@@ -29,7 +29,8 @@
 // When a wait runs out the block records a code in the status word, every role stops, the block
 // frees its tensor memory and returns; the host reads the status word after the step and raises.
 //
-// A token at position p sees keys lo..p, lo = 0 or p - window + 1.  Pages that lie wholly
+// A token at position p sees keys lo..p, lo = 0, p - window + 1, or the start of p's chunk for a
+// window of minus the chunk's size (first_visible()).  Pages that lie wholly
 // outside the tile's range, or that were given back, are never dereferenced; their rows of a
 // stage keep what an earlier tile left there (the V stages start as zeros), and every key outside
 // a row's range is masked.  The page size must be a power of two (pages of 1 .. 128 keys divide
